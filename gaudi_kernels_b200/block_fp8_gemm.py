@@ -1,0 +1,165 @@
+"""Block-scaled E4M3 GEMM on B200 behind the reference oracle's signature.
+
+`reference(x, weight, scales, *, native_half=False, bias=None)` takes the arguments of
+python/gaudi_kernels/block_fp8_oracle.py:11 of tracycam/gaudi-kernels - bf16 activations, the
+original OCP float8_e4m3fn weight [N, K] and its fp32 128x128 scale grid - and returns the bf16
+product, computed by libbfp8.so's kernels: 1x128 activation quantization (:25-28), optional
+half-range adaptation of both operands (:31-35), the per-K-block contraction on the tensor cores
+and the fp32 scale promotion (:38-41), bias (:42-45), bf16 rounding (:46).  Differences from the
+reference, all relaxations: any number of activation rows (the reference insists on one, :16-17),
+and tensors may live on a CUDA device.  Contract breaches raise ValueError as there.
+
+`gemm_block_fp8` is the hot path for operands that are already quantized (weights are prepared
+once at load time; the reference's loader does that with fp8_codec.reencode_e4m3fn_half).
+There is no CPU implementation in this package.
+"""
+
+import torch
+
+from . import _lib
+from .fp8_codec import BLOCK, _device_for, _read_status, _status_buffer, _stream_ptr, quantize_act_1x128
+
+_WAIT_TIMEOUT_MSG = "a bounded wait inside the GEMM kernel expired (BFP8_STATUS_WAIT_TIMEOUT); output is invalid"
+
+
+def _group_major(a_scales, m, g):
+    """Return (tensor, ldsa) with element (row i, group g) at data[g * ldsa + i]."""
+    if tuple(a_scales.shape) != (m, g) or a_scales.dtype != torch.float32:
+        raise ValueError("activation scales must be FP32 [M, ceil(K/128)]")
+    if m == 1 or g == 1:
+        a_scales = a_scales.contiguous() if not a_scales.is_contiguous() else a_scales
+        return a_scales, m
+    if a_scales.stride(0) == 1 and a_scales.stride(1) >= m:
+        return a_scales, a_scales.stride(1)
+    t = a_scales.t().contiguous()          # [G, M]
+    return t, m
+
+
+def gemm_block_fp8(a_codes, a_scales, w_codes, w_scales, bias=None, out=None, out_dtype=torch.bfloat16,
+                   check=True, schedule=0, max_ctas=0, wait_limit_cycles=0):
+    """out[i, j] = sum_g a_scales[i, g] * w_scales[j // 128, g] * <a_codes[i, g-block], w_codes[j, g-block]> (+ bias[j]).
+
+    a_codes  E4M3 [M, K] (float8_e4m3fn or uint8), contiguous, on a CUDA device
+    a_scales fp32 [M, G]; group-major storage (as returned by quantize_act_1x128) avoids a copy
+    w_codes  E4M3 [N, K], contiguous;  w_scales fp32 [ceil(N/128), G] contiguous
+    bias     fp32 [N] or None;  out_dtype torch.bfloat16 (default) or torch.float32
+    check    read the device status word after the launch (one synchronisation) and raise if a
+             bounded wait expired; pass False on a latency-critical path and poll the status yourself
+    """
+    for name, t in (("a_codes", a_codes), ("w_codes", w_codes)):
+        if (not isinstance(t, torch.Tensor) or t.dtype not in (torch.float8_e4m3fn, torch.uint8) or t.ndim != 2
+                or not t.is_contiguous() or t.device.type != "cuda"):
+            raise ValueError("%s must be a contiguous 2-D E4M3 tensor on a CUDA device" % name)
+    m, k = a_codes.shape
+    n = w_codes.shape[0]
+    if w_codes.shape[1] != k or m < 1 or n < 1 or k < 1:
+        raise ValueError("a_codes [M, K] and w_codes [N, K] must share K")
+    g = (k + BLOCK - 1) // BLOCK
+    if (not isinstance(w_scales, torch.Tensor) or w_scales.dtype != torch.float32 or not w_scales.is_contiguous()
+            or tuple(w_scales.shape) != ((n + BLOCK - 1) // BLOCK, g)):
+        raise ValueError("original block128 scale grid mismatch")
+    if out_dtype not in (torch.bfloat16, torch.float32):
+        raise ValueError("out_dtype must be bfloat16 or float32")
+    dev = a_codes.device
+    if bias is not None:
+        if bias.numel() != n:
+            raise ValueError("bias with N elements required")
+        bias = bias.to(device=dev, dtype=torch.float32).contiguous().view(-1)
+    lib = _lib.load()
+    with torch.cuda.device(dev):
+        if k % 16 != 0:
+            # TMA needs 16-byte row pitches: pad K with zero codes (zero contributes nothing).
+            kp = (k + 15) // 16 * 16
+            a_codes = torch.nn.functional.pad(a_codes.view(torch.uint8), (0, kp - k))
+            w_codes = torch.nn.functional.pad(w_codes.view(torch.uint8), (0, kp - k))
+        lda, ldw = a_codes.stride(0), w_codes.stride(0)
+        sa, ldsa = _group_major(a_scales.to(dev), m, g)
+        w_scales = w_scales.to(dev)
+        if out is None:
+            ldo = n if out_dtype == torch.float32 else (n + 7) // 8 * 8
+            storage = torch.empty((m, ldo), dtype=out_dtype, device=dev)
+            out = storage[:, :n]
+        else:
+            if (out.dtype != out_dtype or tuple(out.shape) != (m, n) or out.stride(1) != 1
+                    or out.device != dev):
+                raise ValueError("out must be [M, N] of out_dtype with unit column stride on the operand device")
+            ldo = out.stride(0)
+        ws_bytes = lib.bfp8_gemm_block128_workspace_bytes(m, n, k)
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev) if ws_bytes else None
+        st = _status_buffer(dev)
+        rc = lib.bfp8_gemm_block128_ex(
+            a_codes.data_ptr(), lda, sa.data_ptr(), ldsa, w_codes.data_ptr(), ldw, w_scales.data_ptr(),
+            bias.data_ptr() if bias is not None else None, out.data_ptr(),
+            _lib.OUT_BF16 if out_dtype == torch.bfloat16 else _lib.OUT_F32, ldo, m, n, k,
+            ws.data_ptr() if ws is not None else None, ws_bytes, st.data_ptr() + 8, _stream_ptr(),
+            schedule, max_ctas, wait_limit_cycles)
+        _lib.check(rc, "bfp8_gemm_block128")
+        if check and _read_status(st)[1] & _lib.STATUS_WAIT_TIMEOUT:
+            raise _lib.Bfp8Error(_WAIT_TIMEOUT_MSG)
+    return out
+
+
+def prepare_weight(weight, scales, native_half=True):
+    """Load-time weight preparation: OCP codes + scales -> what gemm_block_fp8 consumes.
+
+    With native_half this is fp8_codec.reencode_e4m3fn_half (python/gaudi_kernels/fp8_codec.py:14-53)
+    on the GPU; otherwise the OCP codes are used as they are.  Returns (codes, scales) on the device.
+    """
+    from .fp8_codec import reencode_e4m3fn_half
+    dev = _device_for(weight, scales)
+    weight, scales = weight.to(dev), scales.to(dev)
+    if native_half:
+        weight, scales, _ = reencode_e4m3fn_half(weight, scales)
+    return weight, scales
+
+
+def reference(x, weight, scales, *, native_half=False, bias=None, out_dtype=torch.bfloat16):
+    """Drop-in for gaudi_kernels.block_fp8_oracle.reference, computed on the GPU.
+
+    x bf16 [M, K]; weight float8_e4m3fn [N, K] (original OCP codes); scales fp32 [ceil(N/128), ceil(K/128)].
+    Host tensors are copied to the current CUDA device and the result is returned on the host.
+    """
+    if (not isinstance(x, torch.Tensor) or not isinstance(weight, torch.Tensor) or not isinstance(scales, torch.Tensor)
+            or x.dtype != torch.bfloat16 or weight.dtype != torch.float8_e4m3fn
+            or scales.dtype != torch.float32 or x.ndim != 2 or weight.ndim != 2
+            or x.shape[0] < 1 or x.shape[1] != weight.shape[1]):
+        raise ValueError("BF16 activation rows, original OCP FP8 weight and FP32 scales required")
+    n, k = weight.shape
+    groups = (k + BLOCK - 1) // BLOCK
+    if tuple(scales.shape) != ((n + BLOCK - 1) // BLOCK, groups):
+        raise ValueError("original block128 scale grid mismatch")
+    if bias is not None and bias.numel() != n:
+        raise ValueError("bias with N elements required")
+    lib = _lib.load()
+    dev = _device_for(x, weight, scales)
+    on_host = x.device.type == "cpu"
+    with torch.cuda.device(dev):
+        xd = x.to(dev, non_blocking=True).contiguous()
+        wd = weight.to(dev, non_blocking=True).contiguous()
+        sd = scales.to(dev, non_blocking=True).contiguous()
+        st = _status_buffer(dev)
+        if native_half:
+            # weight side of block_fp8_oracle.py:31-35; also validates codes and scales
+            enc = torch.empty_like(wd)
+            sw = torch.empty_like(sd)
+            rc = lib.bfp8_reencode_half(wd.data_ptr(), enc.data_ptr(), wd.numel(), sd.data_ptr(), sw.data_ptr(),
+                                        sd.numel(), st.data_ptr(), st.data_ptr() + 8, _stream_ptr())
+            _lib.check(rc, "bfp8_reencode_half")
+            finite = None
+        else:
+            enc, sw = wd, sd
+            finite = ((wd.view(torch.uint8) & 0x7F) != 0x7F).all() & torch.isfinite(sd).all() & (sd >= 0).all()
+        m = xd.shape[0]
+        a_codes = torch.empty((m, k), dtype=torch.uint8, device=dev)
+        a_scales = torch.empty((groups, m), dtype=torch.float32, device=dev)
+        rc = lib.bfp8_quant_act_1x128_bf16(xd.data_ptr(), m, k, xd.stride(0), a_codes.data_ptr(), k,
+                                           a_scales.data_ptr(), 1, m, int(bool(native_half)),
+                                           st.data_ptr() + 8, _stream_ptr())
+        _lib.check(rc, "bfp8_quant_act_1x128_bf16")
+        y = gemm_block_fp8(a_codes, a_scales.t(), enc, sw, bias=bias, out_dtype=out_dtype, check=False)
+        status = _read_status(st)[1]
+        if finite is not None and not bool(finite):
+            status |= _lib.STATUS_NONFINITE_CODE
+        if status & (_lib.STATUS_NONFINITE_CODE | _lib.STATUS_BAD_SCALE | _lib.STATUS_NONFINITE_INPUT):
+            raise ValueError("finite original inputs required")
+    return y.cpu() if on_host else y

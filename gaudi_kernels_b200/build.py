@@ -1,0 +1,68 @@
+"""Build libbfp8.so (the C-ABI CUDA library) in-tree with nvcc for sm_100a.
+
+    python -m gaudi_kernels_b200.build [--force]
+
+nvcc cross-compiles without a GPU.  The shared object is written next to this file; it links the
+CUDA runtime statically and resolves the one driver entry point it needs at run time, so it loads
+on a machine without a GPU driver.
+"""
+
+import os
+import shutil
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(HERE, "csrc")
+INCLUDE = os.path.join(os.path.dirname(HERE), "include")
+LIB = os.path.join(HERE, "libbfp8.so")
+SOURCES = ["codec.cu", "gemm_tcgen05.cu", "gemm_api.cu"]
+ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
+CFLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-I" + INCLUDE, "-I" + CSRC]
+
+
+def _nvcc():
+    exe = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(exe):
+        raise RuntimeError("nvcc not found; libbfp8.so cannot be built")
+    return exe
+
+
+def _deps():
+    files = [os.path.join(CSRC, f) for f in os.listdir(CSRC)] + [os.path.join(INCLUDE, "bfp8.h")]
+    return max(os.path.getmtime(f) for f in files)
+
+
+def up_to_date():
+    return os.path.exists(LIB) and os.path.getmtime(LIB) >= _deps()
+
+
+def build(force=False, verbose=False):
+    """Compile every .cu under csrc/ and link libbfp8.so.  Returns the library path."""
+    if not force and up_to_date():
+        return LIB
+    nvcc = _nvcc()
+    objdir = os.path.join(HERE, "build")
+    os.makedirs(objdir, exist_ok=True)
+    objs = []
+    procs = []
+    for src in SOURCES:
+        obj = os.path.join(objdir, src.replace(".cu", ".o"))
+        cmd = [nvcc] + ARCH_FLAGS + CFLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", os.path.join(CSRC, src), "-o", obj]
+        procs.append((cmd, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
+        objs.append(obj)
+    for cmd, pr in procs:
+        out, _ = pr.communicate()
+        if verbose and out:
+            print(out)
+        if pr.returncode != 0:
+            raise RuntimeError("nvcc failed: %s\n%s" % (" ".join(cmd), out))
+    link = [nvcc] + ARCH_FLAGS + ["-shared", "-cudart", "static", "-o", LIB] + objs
+    res = subprocess.run(link, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if res.returncode != 0:
+        raise RuntimeError("link failed: %s\n%s" % (" ".join(link), res.stdout))
+    return LIB
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))

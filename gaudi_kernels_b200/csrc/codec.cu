@@ -1,0 +1,411 @@
+// E4M3 codec kernels: OCP -> half-range re-encode, 128x128 and 1x128 block-amax quantizers, decode.
+// All four are streaming, HBM-bound byte kernels: 128-bit coalesced accesses, everything else in registers.
+#include "common.cuh"
+
+namespace bfp8 {
+
+thread_local int g_last_cuda_error = 0;
+
+int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+// ---------------------------------------------------------------------------------------------
+// K1  re-encode: 1 byte in, 1 byte out per code.
+// ---------------------------------------------------------------------------------------------
+constexpr int kReencodeThreads = 256;
+constexpr int kReencodeUnroll = 4;     // 4 x 16 B in flight per thread
+
+__device__ __forceinline__ void reencode_vec(uint4& v, uint32_t& inexact, uint32_t& bad) {
+  uint32_t* w = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    bad |= nonfinite_x4(w[i]);
+    inexact += __popc(half_inexact_x4(w[i]));
+    w[i] = half_e4m3x4(w[i]);
+  }
+}
+
+__global__ void __launch_bounds__(kReencodeThreads)
+reencode_half_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, int64_t n, int vec_ok,
+                     unsigned long long* __restrict__ rounded, uint32_t* __restrict__ status) {
+  uint32_t inexact = 0, bad = 0;
+  const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t nthreads = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  int64_t done = 0;
+  if (vec_ok) {
+    const int64_t nvec = n >> 4;
+    const uint4* vin = reinterpret_cast<const uint4*>(in);
+    uint4* vout = reinterpret_cast<uint4*>(out);
+    // Each thread owns kReencodeUnroll vectors per sweep, spaced one grid apart so every warp
+    // access is a contiguous 512 B.
+    for (int64_t base = tid; base < nvec; base += nthreads * kReencodeUnroll) {
+      uint4 v[kReencodeUnroll];
+#pragma unroll
+      for (int u = 0; u < kReencodeUnroll; ++u) {
+        const int64_t i = base + u * nthreads;
+        if (i < nvec) v[u] = __ldcs(vin + i);
+      }
+#pragma unroll
+      for (int u = 0; u < kReencodeUnroll; ++u) {
+        const int64_t i = base + u * nthreads;
+        if (i < nvec) {
+          reencode_vec(v[u], inexact, bad);
+          __stcs(vout + i, v[u]);
+        }
+      }
+    }
+    done = nvec << 4;
+  }
+  for (int64_t i = done + tid; i < n; i += nthreads) {           // ragged tail / unaligned buffers
+    const uint32_t c = in[i];
+    bad |= nonfinite_x4(c | 0x00000000u) & 0xffu;
+    inexact += half_inexact_x4(c) & 1u;
+    out[i] = static_cast<uint8_t>(half_e4m3x4(c));
+  }
+  // one atomic per warp at most
+  inexact = __reduce_add_sync(0xffffffffu, inexact);
+  bad = __reduce_or_sync(0xffffffffu, bad);
+  if ((threadIdx.x & 31) == 0) {
+    if (inexact) atomicAdd(rounded, static_cast<unsigned long long>(inexact));
+    if (bad) atomicOr(status, BFP8_STATUS_NONFINITE_CODE);
+  }
+}
+
+// scales_out = 2 * scales_in with the checks of fp8_codec.py:25-32.
+__global__ void double_scales_kernel(const float* __restrict__ in, float* __restrict__ out, int64_t n,
+                                     uint32_t* __restrict__ status) {
+  bool bad = false;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const float s = in[i];
+    const float d = __fmul_rn(s, 2.0f);
+    bad |= !(s >= 0.0f) || isinf(d) || isnan(d);
+    out[i] = d;
+  }
+  if (__any_sync(0xffffffffu, bad) && (threadIdx.x & 31) == 0) atomicOr(status, BFP8_STATUS_BAD_SCALE);
+}
+
+// ---------------------------------------------------------------------------------------------
+// K2  128x128 block-amax quantizer: one CTA per tile, the 64 KB tile lives in registers
+//     (256 threads x 16 float4), so HBM sees exactly one read and one write per element.
+// ---------------------------------------------------------------------------------------------
+constexpr int kQuantThreads = 256;
+
+template <bool kVec>
+__global__ void __launch_bounds__(kQuantThreads)
+quant_block128_kernel(const float* __restrict__ w, int64_t rows, int64_t cols, int64_t ld,
+                      uint8_t* __restrict__ codes, int64_t ld_codes, float* __restrict__ scales,
+                      int col_blocks, int native_half) {
+  __shared__ float warp_max[kQuantThreads / 32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t r0 = static_cast<int64_t>(blockIdx.y) * 128, c0 = static_cast<int64_t>(blockIdx.x) * 128;
+  const int64_t c = c0 + lane * 4;
+  float4 v[16];
+  float amax = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const int64_t r = r0 + warp + 8 * i;
+    v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (r < rows) {
+      const float* p = w + r * ld + c;
+      if (kVec) {
+        if (c < cols) v[i] = __ldcs(reinterpret_cast<const float4*>(p));   // cols % 4 == 0 on this path
+      } else {
+        if (c + 0 < cols) v[i].x = p[0];
+        if (c + 1 < cols) v[i].y = p[1];
+        if (c + 2 < cols) v[i].z = p[2];
+        if (c + 3 < cols) v[i].w = p[3];
+      }
+    }
+    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[i].x), fabsf(v[i].y)), fmaxf(fabsf(v[i].z), fabsf(v[i].w))));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if (lane == 0) warp_max[warp] = amax;
+  __syncthreads();
+  amax = warp_max[0];
+#pragma unroll
+  for (int i = 1; i < kQuantThreads / 32; ++i) amax = fmaxf(amax, warp_max[i]);
+  const float s = scale_from_amax(amax);
+  if (threadIdx.x == 0)
+    scales[static_cast<int64_t>(blockIdx.y) * col_blocks + blockIdx.x] = native_half ? __fmul_rn(s, 2.0f) : s;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const int64_t r = r0 + warp + 8 * i;
+    if (r >= rows) continue;
+    uint32_t q = cvt_e4m3x4(scaled_clamped(v[i].x, s), scaled_clamped(v[i].y, s),
+                            scaled_clamped(v[i].z, s), scaled_clamped(v[i].w, s));
+    if (native_half) q = half_e4m3x4(q);
+    uint8_t* p = codes + r * ld_codes + c;
+    if (kVec) {
+      if (c < cols) __stcs(reinterpret_cast<uint32_t*>(p), q);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (c + j < cols) p[j] = static_cast<uint8_t>(q >> (8 * j));
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// K3  1x128 activation quantizer: a half-warp (16 lanes x 8 bf16 = 16 B each) owns one group.
+// ---------------------------------------------------------------------------------------------
+constexpr int kActThreads = 256;
+
+template <bool kVec, typename Idx>
+__global__ void __launch_bounds__(kActThreads)
+quant_act_1x128_kernel(const uint16_t* __restrict__ x, int64_t m, int64_t k, int64_t ldx,
+                       uint8_t* __restrict__ codes, int64_t ld_codes, float* __restrict__ scales,
+                       int64_t ssm, int64_t ssg, int64_t groups, int native_half,
+                       uint32_t* __restrict__ status) {
+  const int sub = threadIdx.x & 15;
+  uint32_t nonfinite = 0;                                      // lane inside the half-warp
+  // Idx is 32-bit whenever m * groups fits, which keeps the row/group split cheap.
+  const Idx hw = static_cast<Idx>((static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 4);
+  const Idx nhw = static_cast<Idx>((static_cast<int64_t>(gridDim.x) * blockDim.x) >> 4);
+  const Idx total = static_cast<Idx>(m * groups);
+  const Idx ngroups = static_cast<Idx>(groups);
+  // All 32 lanes of a warp run the same number of iterations (shuffles below are warp-wide).
+  const Idx iters = (total + nhw - 1) / nhw;
+  for (Idx it = 0; it < iters; ++it) {
+    const Idx idx = hw + it * nhw;
+    const bool live = idx < total;
+    const int64_t row = live ? idx / ngroups : 0, g = live ? idx % ngroups : 0;
+    const int64_t col = g * 128 + sub * 8;
+    float f[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] = 0.0f;
+    if (live) {
+      const uint16_t* p = x + row * ldx + col;
+      if (kVec) {
+        if (col < k) {                                                   // k % 8 == 0 on this path
+          const uint4 raw = __ldcs(reinterpret_cast<const uint4*>(p));
+          const uint32_t* r = reinterpret_cast<const uint32_t*>(&raw);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            // a bf16 with all exponent bits set is inf or NaN
+            nonfinite |= __vcmpeq2(r[j] & 0x7f807f80u, 0x7f807f80u);
+            f[2 * j] = bf16_bits_to_float(r[j] & 0xffffu);
+            f[2 * j + 1] = bf16_bits_to_float(r[j] >> 16);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (col + j < k) {
+            nonfinite |= (p[j] & 0x7f80u) == 0x7f80u;
+            f[j] = bf16_bits_to_float(p[j]);
+          }
+      }
+    }
+    float amax = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(f[j]));
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float s = scale_from_amax(amax);
+    uint32_t q0 = cvt_e4m3x4(scaled_clamped(f[0], s), scaled_clamped(f[1], s),
+                             scaled_clamped(f[2], s), scaled_clamped(f[3], s));
+    uint32_t q1 = cvt_e4m3x4(scaled_clamped(f[4], s), scaled_clamped(f[5], s),
+                             scaled_clamped(f[6], s), scaled_clamped(f[7], s));
+    if (native_half) { q0 = half_e4m3x4(q0); q1 = half_e4m3x4(q1); }
+    if (live) {
+      uint8_t* p = codes + row * ld_codes + col;
+      if (kVec) {
+        if (col < k) __stcs(reinterpret_cast<uint2*>(p), make_uint2(q0, q1));
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (col + j < k) p[j] = static_cast<uint8_t>((j < 4 ? q0 : q1) >> (8 * (j & 3)));
+      }
+      if (sub == 0) scales[row * ssm + g * ssg] = native_half ? __fmul_rn(s, 2.0f) : s;
+    }
+  }
+  if (status != nullptr && __any_sync(0xffffffffu, nonfinite != 0) && (threadIdx.x & 31) == 0)
+    atomicOr(status, BFP8_STATUS_NONFINITE_INPUT);
+}
+
+// ---------------------------------------------------------------------------------------------
+// K4  decode: value(code) * block scale.  A thread turns 4 codes (one 32-bit load) into one
+//     16-byte (fp32) or 8-byte (bf16) store, so both sides of every warp access are contiguous.
+// ---------------------------------------------------------------------------------------------
+constexpr int kDecodeThreads = 256;
+
+template <bool kVec, bool kBf16, typename Idx>
+__global__ void __launch_bounds__(kDecodeThreads)
+decode_block128_kernel(const uint8_t* __restrict__ codes, int64_t rows, int64_t cols, int64_t ld,
+                       const float* __restrict__ scales, int col_blocks, void* __restrict__ out,
+                       int64_t ld_out) {
+  // Idx is 32-bit whenever rows * ceil(cols/4) fits, which keeps the row/column split cheap.
+  const Idx quads_per_row = static_cast<Idx>((cols + 3) >> 2);
+  const Idx total = static_cast<Idx>(rows) * quads_per_row;
+  const Idx step = static_cast<Idx>(gridDim.x) * blockDim.x;
+  for (Idx i = static_cast<Idx>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += step) {
+    const int64_t r = i / quads_per_row, c = static_cast<int64_t>(i % quads_per_row) << 2;
+    const float s = __ldg(scales + (r >> 7) * col_blocks + (c >> 7));
+    const uint8_t* p = codes + r * ld + c;
+    uint32_t q = 0;
+    if (kVec) {
+      q = __ldcs(reinterpret_cast<const uint32_t*>(p));
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (c + j < cols) q |= static_cast<uint32_t>(p[j]) << (8 * j);
+    }
+    const float2 lo = e4m3x2_to_float2(q & 0xffffu), hi = e4m3x2_to_float2(q >> 16);
+    const float v0 = __fmul_rn(lo.x, s), v1 = __fmul_rn(lo.y, s), v2 = __fmul_rn(hi.x, s), v3 = __fmul_rn(hi.y, s);
+    if (kBf16) {
+      uint16_t* o = reinterpret_cast<uint16_t*>(out) + r * ld_out + c;
+      if (kVec) {
+        __stcs(reinterpret_cast<uint2*>(o), make_uint2(pack_bf16x2(v0, v1), pack_bf16x2(v2, v3)));
+      } else {
+        const float v[4] = {v0, v1, v2, v3};
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (c + j < cols) o[j] = static_cast<uint16_t>(float_to_bf16_bits(v[j]));
+      }
+    } else {
+      float* o = reinterpret_cast<float*>(out) + r * ld_out + c;
+      if (kVec) {
+        __stcs(reinterpret_cast<float4*>(o), make_float4(v0, v1, v2, v3));
+      } else {
+        const float v[4] = {v0, v1, v2, v3};
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (c + j < cols) o[j] = v[j];
+      }
+    }
+  }
+}
+
+int grid_for(int64_t work_items, int threads, int max_ctas_per_sm) {
+  const int64_t want = (work_items + threads - 1) / threads;
+  const int64_t cap = static_cast<int64_t>(sm_count()) * max_ctas_per_sm;
+  return static_cast<int>(want < 1 ? 1 : (want < cap ? want : cap));
+}
+
+}  // namespace bfp8
+
+using namespace bfp8;
+
+extern "C" int bfp8_version(void) { return 1; }
+
+extern "C" int bfp8_last_cuda_error(void) { return g_last_cuda_error; }
+
+extern "C" const char* bfp8_error_string(int code) {
+  switch (code) {
+    case BFP8_OK: return "ok";
+    case BFP8_ERR_NULL: return "null pointer";
+    case BFP8_ERR_ALIGN: return "pointer or leading dimension is misaligned";
+    case BFP8_ERR_SHAPE: return "size out of range";
+    case BFP8_ERR_WORKSPACE: return "workspace too small";
+    case BFP8_ERR_CUDA: return "CUDA call failed";
+    case BFP8_ERR_UNSUPPORTED: return "device is not sm_100";
+    default: return "unknown error";
+  }
+}
+
+extern "C" int bfp8_reencode_half(const uint8_t* codes_in, uint8_t* codes_out, int64_t n,
+                                  const float* scales_in, float* scales_out, int64_t n_scales,
+                                  unsigned long long* rounded_dev, uint32_t* status_dev, void* stream) {
+  if (!codes_in || !codes_out || !rounded_dev || !status_dev) return BFP8_ERR_NULL;
+  if (n <= 0 || n_scales < 0) return BFP8_ERR_SHAPE;
+  if (n_scales > 0 && (!scales_in || !scales_out)) return BFP8_ERR_NULL;
+  if (!aligned(rounded_dev, 8) || !aligned(status_dev, 4)) return BFP8_ERR_ALIGN;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int vec_ok = aligned(codes_in, 16) && aligned(codes_out, 16);
+  const int grid = grid_for((n + 15) / 16 / kReencodeUnroll + 1, kReencodeThreads, 8);
+  reencode_half_kernel<<<grid, kReencodeThreads, 0, st>>>(codes_in, codes_out, n, vec_ok, rounded_dev, status_dev);
+  BFP8_CUDA_TRY(cudaGetLastError());
+  if (n_scales > 0) {
+    double_scales_kernel<<<grid_for(n_scales, 256, 4), 256, 0, st>>>(scales_in, scales_out, n_scales, status_dev);
+    BFP8_CUDA_TRY(cudaGetLastError());
+  }
+  return BFP8_OK;
+}
+
+extern "C" int bfp8_quant_block128_f32(const float* w, int64_t rows, int64_t cols, int64_t ld,
+                                       uint8_t* codes, int64_t ld_codes, float* scales,
+                                       int native_half, void* stream) {
+  if (!w || !codes || !scales) return BFP8_ERR_NULL;
+  if (rows <= 0 || cols <= 0 || ld < cols || ld_codes < cols) return BFP8_ERR_SHAPE;
+  const int64_t rb = (rows + 127) / 128, cb = (cols + 127) / 128;
+  if (rb > 65535 || cb > 2147483647LL) return BFP8_ERR_SHAPE;
+  if (!aligned(w, 4) || !aligned(scales, 4)) return BFP8_ERR_ALIGN;
+  const bool vec = aligned(w, 16) && aligned(codes, 4) && ld % 4 == 0 && ld_codes % 4 == 0 && cols % 4 == 0;
+  dim3 grid(static_cast<unsigned>(cb), static_cast<unsigned>(rb));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (vec)
+    quant_block128_kernel<true><<<grid, kQuantThreads, 0, st>>>(w, rows, cols, ld, codes, ld_codes, scales,
+                                                                static_cast<int>(cb), native_half);
+  else
+    quant_block128_kernel<false><<<grid, kQuantThreads, 0, st>>>(w, rows, cols, ld, codes, ld_codes, scales,
+                                                                 static_cast<int>(cb), native_half);
+  BFP8_CUDA_TRY(cudaGetLastError());
+  return BFP8_OK;
+}
+
+extern "C" int bfp8_quant_act_1x128_bf16(const uint16_t* x, int64_t m, int64_t k, int64_t ldx,
+                                         uint8_t* codes, int64_t ld_codes,
+                                         float* scales, int64_t scale_stride_m, int64_t scale_stride_g,
+                                         int native_half, uint32_t* status_dev, void* stream) {
+  if (!x || !codes || !scales) return BFP8_ERR_NULL;
+  if (m <= 0 || k <= 0 || ldx < k || ld_codes < k || scale_stride_m <= 0 || scale_stride_g <= 0)
+    return BFP8_ERR_SHAPE;
+  if (!aligned(x, 2) || !aligned(scales, 4)) return BFP8_ERR_ALIGN;
+  const int64_t groups = (k + 127) / 128;
+  const bool vec = aligned(x, 16) && aligned(codes, 8) && ldx % 8 == 0 && ld_codes % 8 == 0 && k % 8 == 0;
+  const int grid = grid_for(m * groups * 16, kActThreads, 8);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const bool small = m * groups < (1LL << 30);
+#define BFP8_LAUNCH_ACT(V, I)                                                                        \
+  quant_act_1x128_kernel<V, I><<<grid, kActThreads, 0, st>>>(x, m, k, ldx, codes, ld_codes, scales,  \
+                                                             scale_stride_m, scale_stride_g, groups, native_half, \
+                                                             status_dev)
+  if (vec && small) BFP8_LAUNCH_ACT(true, uint32_t);
+  else if (vec) BFP8_LAUNCH_ACT(true, int64_t);
+  else if (small) BFP8_LAUNCH_ACT(false, uint32_t);
+  else BFP8_LAUNCH_ACT(false, int64_t);
+#undef BFP8_LAUNCH_ACT
+  BFP8_CUDA_TRY(cudaGetLastError());
+  return BFP8_OK;
+}
+
+extern "C" int bfp8_decode_block128(const uint8_t* codes, int64_t rows, int64_t cols, int64_t ld,
+                                    const float* scales, void* out, int out_dtype, int64_t ld_out,
+                                    void* stream) {
+  if (!codes || !scales || !out) return BFP8_ERR_NULL;
+  if (rows <= 0 || cols <= 0 || ld < cols || ld_out < cols) return BFP8_ERR_SHAPE;
+  if (out_dtype != BFP8_OUT_F32 && out_dtype != BFP8_OUT_BF16) return BFP8_ERR_SHAPE;
+  const bool bf16 = out_dtype == BFP8_OUT_BF16;
+  if (!aligned(out, bf16 ? 2 : 4) || !aligned(scales, 4)) return BFP8_ERR_ALIGN;
+  const int cb = static_cast<int>((cols + 127) / 128);
+  const bool vec = aligned(codes, 4) && ld % 4 == 0 && cols % 4 == 0 && ld_out % 4 == 0 &&
+                   aligned(out, bf16 ? 8 : 16);
+  const int grid = grid_for(rows * ((cols + 3) / 4), kDecodeThreads, 8);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const bool small = rows * ((cols + 3) / 4) < (1LL << 30);
+#define BFP8_LAUNCH_DECODE(V, B)                                                                            \
+  do {                                                                                                      \
+    if (small)                                                                                              \
+      decode_block128_kernel<V, B, uint32_t><<<grid, kDecodeThreads, 0, st>>>(codes, rows, cols, ld, scales, cb, out, ld_out); \
+    else                                                                                                    \
+      decode_block128_kernel<V, B, int64_t><<<grid, kDecodeThreads, 0, st>>>(codes, rows, cols, ld, scales, cb, out, ld_out);  \
+  } while (0)
+  if (vec && bf16) BFP8_LAUNCH_DECODE(true, true);
+  else if (vec) BFP8_LAUNCH_DECODE(true, false);
+  else if (bf16) BFP8_LAUNCH_DECODE(false, true);
+  else BFP8_LAUNCH_DECODE(false, false);
+#undef BFP8_LAUNCH_DECODE
+  BFP8_CUDA_TRY(cudaGetLastError());
+  return BFP8_OK;
+}

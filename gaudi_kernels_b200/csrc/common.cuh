@@ -1,0 +1,103 @@
+// Shared helpers for the libbfp8 kernels (sm_100a only).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "bfp8.h"
+
+namespace bfp8 {
+
+// Per-thread record of the last failing CUDA call, readable through bfp8_last_cuda_error().
+extern thread_local int g_last_cuda_error;
+
+inline int cuda_fail(cudaError_t e) {
+  g_last_cuda_error = static_cast<int>(e);
+  return BFP8_ERR_CUDA;
+}
+
+#define BFP8_CUDA_TRY(expr)                                   \
+  do {                                                        \
+    cudaError_t e_ = (expr);                                  \
+    if (e_ != cudaSuccess) return ::bfp8::cuda_fail(e_);      \
+  } while (0)
+
+inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+
+// Number of SMs of the current device (cached per device id).
+int sm_count();
+
+// ---- E4M3 byte arithmetic -----------------------------------------------------------------
+
+// Half of four packed OCP E4M3FN codes, round-to-nearest-even, in the Gaudi2 encoding
+// (the byte map of python/gaudi_kernels/fp8_codec.py:36-40 evaluated on four bytes at once):
+// magnitude >= 16 loses one exponent step (magnitude - 8); below that the significand shifts right
+// by one and an odd magnitude rounds up only when the shifted value is odd.
+__device__ __forceinline__ uint32_t half_e4m3x4(uint32_t w) {
+  const uint32_t mag = w & 0x7f7f7f7fu;
+  const uint32_t ge16 = __vcmpgeu4(mag, 0x10101010u);            // 0xff in bytes with magnitude >= 16
+  const uint32_t hi = __vsub4(mag, 0x08080808u);
+  const uint32_t sh = (mag >> 1) & 0x7f7f7f7fu;
+  const uint32_t lo = sh + (mag & sh & 0x01010101u);
+  return (w & 0x80808080u) | (hi & ge16) | (lo & ~ge16);
+}
+
+// Bit 0 of each byte set where halving that code is inexact (magnitude < 16 and odd).
+__device__ __forceinline__ uint32_t half_inexact_x4(uint32_t w) {
+  const uint32_t mag = w & 0x7f7f7f7fu;
+  return mag & 0x01010101u & ~__vcmpgeu4(mag, 0x10101010u);
+}
+
+// Non-zero where a byte is 0x7f or 0xff.
+__device__ __forceinline__ uint32_t nonfinite_x4(uint32_t w) {
+  return __vcmpeq4(w & 0x7f7f7f7fu, 0x7f7f7f7fu);
+}
+
+// Two fp32 -> two OCP E4M3 codes (RNE, finite saturation), `lo` in bits 0-7.
+__device__ __forceinline__ uint32_t cvt_e4m3x2(float lo, float hi) {
+  uint16_t r;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
+__device__ __forceinline__ uint32_t cvt_e4m3x4(float a, float b, float c, float d) {
+  return cvt_e4m3x2(a, b) | (cvt_e4m3x2(c, d) << 16);
+}
+
+// Two OCP E4M3 codes (bits 0-15) -> two fp32, exact.
+__device__ __forceinline__ float2 e4m3x2_to_float2(uint32_t v) {
+  uint32_t h2;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"(static_cast<uint16_t>(v)));
+  float lo, hi;
+  asm("{.reg .f16 l, h; mov.b32 {l, h}, %2; cvt.f32.f16 %0, l; cvt.f32.f16 %1, h;}"
+      : "=f"(lo), "=f"(hi) : "r"(h2));
+  return make_float2(lo, hi);
+}
+
+// The activation / weight scale rule of block_fp8_oracle.py:27: max(amax, 1e-10) * fp32(1/448),
+// one fp32 multiply rounded to nearest (no contraction).
+__device__ __forceinline__ float scale_from_amax(float amax) {
+  return __fmul_rn(fmaxf(amax, 1e-10f), static_cast<float>(1.0 / 448.0));
+}
+
+// block_fp8_oracle.py:28: IEEE fp32 division, clamp to +-448.
+__device__ __forceinline__ float scaled_clamped(float x, float scale) {
+  return fminf(fmaxf(__fdiv_rn(x, scale), -448.0f), 448.0f);
+}
+
+__device__ __forceinline__ float bf16_bits_to_float(uint32_t b) { return __uint_as_float(b << 16); }
+
+// fp32 -> bf16 bits, round-to-nearest-even (finite inputs and NaN-preserving).
+__device__ __forceinline__ uint32_t float_to_bf16_bits(float f) {
+  uint16_t r;
+  asm("cvt.rn.bf16.f32 %0, %1;" : "=h"(r) : "f"(f));
+  return r;
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
+}  // namespace bfp8

@@ -1,0 +1,356 @@
+// Block-scaled E4M3 GEMM for sm_100a: TMA -> shared memory -> tcgen05.mma (kind::f8f6f4) -> TMEM,
+// with the per-128-K-block fp32 scale promotion done by the epilogue warps.
+//
+//   out[i, j] = sum_g sa[g, i] * sw[j/128, g] * ( A_g[i, :] . W_g[j, :] )      A_g, W_g: 128 codes wide
+//
+// One K block (128 E4M3 codes = 128 bytes per row) is exactly one SWIZZLE_128B shared-memory row, so a
+// pipeline stage holds one K block of a 128-row A tile and a 256-row W tile, and four K=32 MMAs
+// consume it.  Because the scale product changes with every K block, each block is accumulated from
+// zero into one of two 256-column TMEM buffers; the epilogue warps read it back (tcgen05.ld), fold
+// it into register accumulators with one FMA per element, and hand the buffer back, while the MMA
+// warp is already filling the other buffer.
+//
+// Warp roles (384 threads): warps 0-7 epilogue (two warpgroups; warpgroup w owns output columns
+// 128w..128w+127 of the tile, so it sees a single weight scale per K block), warp 8 TMA producer,
+// warp 9 TMEM owner and MMA issuer (warps 10-11 idle; the third warpgroup gives its registers to the
+// epilogue through setmaxnreg).  The kernel is persistent: one CTA per SM walks a static tile
+// list.  Every barrier wait is bounded; on expiry the CTA raises BFP8_STATUS_WAIT_TIMEOUT and leaves.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace bfp8 {
+
+namespace {
+
+constexpr int BM = 128;            // tile rows (A rows, TMEM lanes)
+constexpr int BN = 256;            // tile columns (W rows, TMEM columns per buffer)
+constexpr int BK = 128;            // one scale block of K
+constexpr int kStages = 3;
+constexpr int kEpiWarps = 8;
+constexpr int kThreads = (kEpiWarps + 4) * 32;   // warps 10, 11 only complete the third warpgroup
+constexpr int kTmemCols = 512;     // two accumulator buffers of BN columns
+
+constexpr int kABytes = BM * BK;               // 16 KB
+constexpr int kBBytes = BN * BK;               // 32 KB
+constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kOutStageBytes = kEpiWarps * 32 * 128 * 2;   // per warp: 32 rows x 128 bf16
+
+struct SmemTail {
+  uint64_t full[kStages];
+  uint64_t empty[kStages];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  uint32_t abort_flag;
+};
+
+constexpr int kSmemBytes = 1024 /* alignment slack */ + kStages * kStageBytes + kOutStageBytes + sizeof(SmemTail);
+
+struct GemmParams {
+  const float* a_scales;   // [G, ldsa]
+  const float* w_scales;   // [NB, G]
+  const float* bias;       // [N] or null
+  void* out;               // fp32 or bf16 [M, ldo]
+  int64_t ldsa, ldo;
+  int m, n, k, groups;
+  int tiles_m, tiles_n;
+  long long wait_limit;
+  uint32_t* status;
+};
+
+// Tiles are walked in bands of 8 tile-rows: consecutive tile indices share W tiles inside a band,
+// so the CTAs running at any moment touch a compact set of A and W tiles in L2.
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& tm, int& tn) {
+  constexpr int kBand = 8;
+  const int per_band = kBand * tiles_n;
+  const int band = t / per_band;
+  const int first = band * kBand;
+  const int rows = min(kBand, tiles_m - first);
+  const int r = t - band * per_band;
+  tm = first + r % rows;
+  tn = r / rows;
+}
+
+template <bool kOutBf16>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_block128_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
+                     const __grid_constant__ CUtensorMap tmap_out, const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
+  uint8_t* out_stage = smem + kStages * kStageBytes;
+  SmemTail* tail = reinterpret_cast<SmemTail*>(out_stage + kOutStageBytes);
+  volatile uint32_t* abort_flag = &tail->abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int G = p.groups;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      ptx::mbar_init(ptx::smem_u32(&tail->full[s]), 1);
+      ptx::mbar_init(ptx::smem_u32(&tail->empty[s]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      ptx::mbar_init(ptx::smem_u32(&tail->tmem_full[b]), 1);
+      ptx::mbar_init(ptx::smem_u32(&tail->tmem_empty[b]), kEpiWarps);
+    }
+    tail->abort_flag = 0;
+    ptx::fence_mbar_init();
+  }
+  if (warp == kEpiWarps + 1) {
+    ptx::tmem_alloc(ptx::smem_u32(&tail->tmem_base), kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  if (warp == kEpiWarps && lane == 0) {
+    ptx::prefetch_tensormap(&tmap_a);
+    ptx::prefetch_tensormap(&tmap_w);
+    if (kOutBf16) ptx::prefetch_tensormap(&tmap_out);
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = tail->tmem_base;
+
+  if (warp >= kEpiWarps) {
+   ptx::setmaxnreg_dec<40>();
+   if (warp == kEpiWarps) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int tm, tn;
+        tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+        for (int g = 0; g < G; ++g) {
+          ok = ptx::mbar_wait(ptx::smem_u32(&tail->empty[stage]), phase ^ 1u, abort_flag, p.wait_limit);
+          if (!ok) break;
+          const uint32_t full = ptx::smem_u32(&tail->full[stage]);
+          const uint32_t a_dst = smem_base + stage * kStageBytes;
+          ptx::mbar_arrive_expect_tx(full, kStageBytes);
+          ptx::tma_load_2d(a_dst, &tmap_a, full, g * BK, tm * BM);
+          ptx::tma_load_2d(a_dst + kABytes, &tmap_w, full, g * BK, tn * BN);
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == kEpiWarps + 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = ptx::umma_idesc_e4m3(BM, BN);
+      uint32_t stage = 0, phase = 0, kb = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        for (int g = 0; g < G; ++g, ++kb) {
+          const uint32_t buf = kb & 1u, acc_phase = (kb >> 1) & 1u;
+          ok = ptx::mbar_wait(ptx::smem_u32(&tail->tmem_empty[buf]), acc_phase ^ 1u, abort_flag, p.wait_limit) &&
+               ptx::mbar_wait(ptx::smem_u32(&tail->full[stage]), phase, abort_flag, p.wait_limit);
+          if (!ok) break;
+          ptx::tc_fence_after_sync();
+          const uint32_t a_addr = smem_base + stage * kStageBytes;
+          const uint64_t a_desc = ptx::umma_desc_k128(a_addr);
+          const uint64_t b_desc = ptx::umma_desc_k128(a_addr + kABytes);
+          const uint32_t d = tmem_base + buf * BN;
+#pragma unroll
+          for (int k4 = 0; k4 < BK / 32; ++k4)   // +32 bytes along K = +2 in the descriptor's address field
+            ptx::umma_f8(d, a_desc + 2u * k4, b_desc + 2u * k4, idesc, k4 > 0);
+          ptx::umma_commit(ptx::smem_u32(&tail->empty[stage]));
+          ptx::umma_commit(ptx::smem_u32(&tail->tmem_full[buf]));
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+   }
+  } else {
+    ptx::setmaxnreg_inc<232>();
+    // ------------------------------------------------------------------ epilogue / promotion
+    const int wg = warp >> 2;                      // column half of the tile
+    const int quad = warp & 3;                     // TMEM lane quarter this warp may read
+    const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
+    uint8_t* my_stage = out_stage + warp * (32 * 128 * 2);
+    uint32_t kb = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      int tm, tn;
+      tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+      const int row = tm * BM + quad * 32 + lane;
+      const int col0 = tn * BN + wg * 128;
+      const bool row_ok = row < p.m;
+      const int nb = col0 >> 7;
+      const bool nb_ok = col0 < p.n;
+      const float* sa_ptr = p.a_scales + row;
+      const float* sw_ptr = p.w_scales + static_cast<int64_t>(nb) * G;
+      float acc[128];
+#pragma unroll
+      for (int j = 0; j < 128; ++j) acc[j] = 0.0f;
+      // scale products are fetched two K blocks ahead of their use
+      float s0 = (row_ok && nb_ok) ? __ldg(sa_ptr) * __ldg(sw_ptr) : 0.0f;
+      float s1 = (row_ok && nb_ok && G > 1) ? __ldg(sa_ptr + p.ldsa) * __ldg(sw_ptr + 1) : 0.0f;
+      for (int g = 0; g < G; ++g, ++kb) {
+        float s2 = 0.0f;
+        if (row_ok && nb_ok && g + 2 < G) s2 = __ldg(sa_ptr + static_cast<int64_t>(g + 2) * p.ldsa) * __ldg(sw_ptr + g + 2);
+        const uint32_t buf = kb & 1u, acc_phase = (kb >> 1) & 1u;
+        ok = ptx::mbar_wait(ptx::smem_u32(&tail->tmem_full[buf]), acc_phase, abort_flag, p.wait_limit);
+        if (!ok) break;
+        ptx::tc_fence_after_sync();
+        const uint32_t taddr = tmem_base + lane_addr + buf * BN + wg * 128;
+        uint32_t ra[16], rb[16];
+        ptx::tmem_ld16(taddr, ra);
+        ptx::tmem_wait_ld16(ra);
+#pragma unroll
+        for (int c = 0; c < 8; c += 2) {
+          ptx::tmem_ld16(taddr + (c + 1) * 16, rb);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) acc[c * 16 + j] = fmaf(__uint_as_float(ra[j]), s0, acc[c * 16 + j]);
+          ptx::tmem_wait_ld16(rb);
+          if (c + 2 < 8) ptx::tmem_ld16(taddr + (c + 2) * 16, ra);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) acc[(c + 1) * 16 + j] = fmaf(__uint_as_float(rb[j]), s0, acc[(c + 1) * 16 + j]);
+          if (c + 2 < 8) ptx::tmem_wait_ld16(ra);
+        }
+        ptx::tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&tail->tmem_empty[buf]));
+        s0 = s1;
+        s1 = s2;
+      }
+      if (!ok) break;
+      // ---- tile done: bias, rounding, store
+      if (p.bias != nullptr) {
+#pragma unroll
+        for (int j = 0; j < 128; ++j)
+          if (col0 + j < p.n) acc[j] += __ldg(p.bias + col0 + j);
+      }
+      if (kOutBf16) {
+        // the previous tile's TMA stores must have finished reading this warp's staging buffer
+        if (lane == 0) ptx::tma_store_wait_read_all();
+        __syncwarp();
+        // two boxes of 32 rows x 64 bf16 (128 B per row), 16-byte chunks XOR-swizzled by row & 7
+#pragma unroll
+        for (int b = 0; b < 2; ++b) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int e = b * 64 + j * 8;
+            uint4 v;
+            v.x = pack_bf16x2(acc[e + 0], acc[e + 1]);
+            v.y = pack_bf16x2(acc[e + 2], acc[e + 3]);
+            v.z = pack_bf16x2(acc[e + 4], acc[e + 5]);
+            v.w = pack_bf16x2(acc[e + 6], acc[e + 7]);
+            *reinterpret_cast<uint4*>(my_stage + b * 4096 + lane * 128 + ((j ^ (lane & 7)) << 4)) = v;
+          }
+        }
+        ptx::fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          const int y = tm * BM + quad * 32;
+          if (y < p.m) {
+            if (col0 < p.n) ptx::tma_store_2d(&tmap_out, ptx::smem_u32(my_stage), col0, y);
+            if (col0 + 64 < p.n) ptx::tma_store_2d(&tmap_out, ptx::smem_u32(my_stage + 4096), col0 + 64, y);
+          }
+          ptx::tma_store_commit();
+        }
+      } else {
+        if (row_ok) {
+          float* o = reinterpret_cast<float*>(p.out) + static_cast<int64_t>(row) * p.ldo + col0;
+#pragma unroll
+          for (int j = 0; j < 128; ++j)
+            if (col0 + j < p.n) o[j] = acc[j];
+        }
+      }
+    }
+    if (kOutBf16 && lane == 0) ptx::tma_store_wait_all();
+  }
+
+  // ------------------------------------------------------------------ teardown
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  if (warp == kEpiWarps + 1) ptx::tmem_dealloc(tmem_base, kTmemCols);
+  if (threadIdx.x == 0 && tail->abort_flag != 0) atomicOr(p.status, BFP8_STATUS_WAIT_TIMEOUT);
+}
+
+// ---- host side ------------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver entry point is looked up at run time so the library has no link-time dependency on libcuda.
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+
+int make_map_2d(CUtensorMap* map, CUtensorMapDataType dt, int elem_bytes, const void* base, uint64_t inner,
+                uint64_t outer, uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (fn == nullptr) return BFP8_ERR_CUDA;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {row_stride_bytes};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  (void)elem_bytes;
+  CUresult r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    g_last_cuda_error = static_cast<int>(r);
+    return BFP8_ERR_CUDA;
+  }
+  return BFP8_OK;
+}
+
+}  // namespace
+
+int launch_gemm_large(const uint8_t* a_codes, int64_t lda, const float* a_scales, int64_t ldsa,
+                      const uint8_t* w_codes, int64_t ldw, const float* w_scales, const float* bias, void* out,
+                      int out_dtype, int64_t ldo, int64_t m, int64_t n, int64_t k, uint32_t* status_dev,
+                      long long wait_limit, int max_ctas, cudaStream_t st) {
+  alignas(64) CUtensorMap tmap_a, tmap_w, tmap_out;
+  int rc = make_map_2d(&tmap_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a_codes, k, m, lda, BK, BM);
+  if (rc != BFP8_OK) return rc;
+  rc = make_map_2d(&tmap_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w_codes, k, n, ldw, BK, BN);
+  if (rc != BFP8_OK) return rc;
+  const bool bf16 = out_dtype == BFP8_OUT_BF16;
+  if (bf16) {
+    rc = make_map_2d(&tmap_out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, out, n, m, ldo * 2, 64, 32);
+    if (rc != BFP8_OK) return rc;
+  } else {
+    tmap_out = tmap_a;   // unused on the fp32 path
+  }
+  GemmParams p;
+  p.a_scales = a_scales;
+  p.w_scales = w_scales;
+  p.bias = bias;
+  p.out = out;
+  p.ldsa = ldsa;
+  p.ldo = ldo;
+  p.m = static_cast<int>(m);
+  p.n = static_cast<int>(n);
+  p.k = static_cast<int>(k);
+  p.groups = static_cast<int>((k + BK - 1) / BK);
+  p.tiles_m = static_cast<int>((m + BM - 1) / BM);
+  p.tiles_n = static_cast<int>((n + BN - 1) / BN);
+  p.wait_limit = wait_limit;
+  p.status = status_dev;
+  const int tiles = p.tiles_m * p.tiles_n;
+  int grid = sm_count();
+  if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
+  if (tiles < grid) grid = tiles;
+  auto kern = bf16 ? gemm_block128_kernel<true> : gemm_block128_kernel<false>;
+  BFP8_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+  kern<<<grid, kThreads, kSmemBytes, st>>>(tmap_a, tmap_w, tmap_out, p);
+  BFP8_CUDA_TRY(cudaGetLastError());
+  return BFP8_OK;
+}
+
+}  // namespace bfp8

@@ -1,0 +1,135 @@
+/* bfp8.h - C ABI of libbfp8.so: block-scaled E4M3 GEMM and E4M3 codec kernels for NVIDIA B200.
+ *
+ * Conventions (all entry points):
+ *   - extern "C", plain pointers and 64-bit sizes; no C++ or framework types cross the boundary.
+ *   - Every pointer named *_dev (and every data pointer) is a device pointer on the current
+ *     CUDA device; `stream` is a cudaStream_t passed as void* (NULL = default stream).
+ *   - The return value is 0 or a negative BFP8_ERR_* code for conditions the host can see
+ *     (null pointer, misalignment, bad shape, workspace too small).  Nothing is launched when an
+ *     error is returned.  Work is enqueued asynchronously on `stream`.
+ *   - Conditions only the device can see are OR-ed into a caller-owned 32-bit status word
+ *     (BFP8_STATUS_* bits).  The caller zeroes it before the first call and reads it after
+ *     synchronising; several calls may share one word.
+ *   - The library keeps no mutable global state except a per-process cache of driver entry
+ *     points; calls are re-entrant and may be issued from several host threads on different streams.
+ *
+ * These conventions mirror the reference glue's: integer status codes instead of exceptions, caller-owned
+ * buffers, and a size query before any call that needs scratch (two-phase protocol of
+ * csrc/host/generic_attention_glue.hpp:84-90 in tracycam/gaudi-kernels).
+ */
+#ifndef BFP8_H_
+#define BFP8_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define BFP8_OK               0
+#define BFP8_ERR_NULL        -1   /* a required pointer is NULL */
+#define BFP8_ERR_ALIGN       -2   /* a pointer or leading dimension breaks the stated alignment */
+#define BFP8_ERR_SHAPE       -3   /* a size is zero, negative or outside the supported range */
+#define BFP8_ERR_WORKSPACE   -4   /* workspace smaller than bfp8_*_workspace_bytes() */
+#define BFP8_ERR_CUDA        -5   /* a CUDA runtime / driver call failed (see bfp8_last_cuda_error) */
+#define BFP8_ERR_UNSUPPORTED -6   /* the device is not an sm_100 part */
+
+#define BFP8_STATUS_NONFINITE_CODE 0x1u  /* an input byte was 0x7f or 0xff (OCP E4M3FN NaN) */
+#define BFP8_STATUS_BAD_SCALE      0x2u  /* a scale was negative, non-finite, or overflowed when doubled */
+#define BFP8_STATUS_WAIT_TIMEOUT   0x4u  /* a bounded barrier wait inside a kernel gave up */
+#define BFP8_STATUS_NONFINITE_INPUT 0x8u /* an activation was inf or NaN */
+
+#define BFP8_OUT_F32  0
+#define BFP8_OUT_BF16 1
+
+int bfp8_version(void);
+const char* bfp8_error_string(int code);
+/* cudaError_t value of the most recent failing CUDA call on this host thread (0 if none). */
+int bfp8_last_cuda_error(void);
+
+/* OCP E4M3FN -> Gaudi2 half-range E4M3 byte map, with the scale doubling that goes with it.
+ * Replaces gaudi_kernels.fp8_codec.reencode_e4m3fn_half (python/gaudi_kernels/fp8_codec.py:14-53):
+ *   codes_out[i] = sign | half(magnitude) with round-to-nearest-even on the low end (:36-40);
+ *   scales_out[j] = 2 * scales_in[j] (:30);
+ *   *rounded_dev += number of codes whose halving was inexact (:50)  (caller zeroes it first);
+ *   status |= NONFINITE_CODE for any 0x7f/0xff (:48-49), BAD_SCALE for the conditions of :25-32.
+ * n > 0 codes; n_scales may be 0 (then scales_* may be NULL).  In-place (codes_out == codes_in) is allowed. */
+int bfp8_reencode_half(const uint8_t* codes_in, uint8_t* codes_out, int64_t n,
+                       const float* scales_in, float* scales_out, int64_t n_scales,
+                       unsigned long long* rounded_dev, uint32_t* status_dev, void* stream);
+
+/* 128x128 block-amax quantizer, fp32 [rows, cols] (row stride ld, elements) -> E4M3 codes
+ * [rows, cols] (row stride ld_codes) + fp32 scales [ceil(rows/128), ceil(cols/128)] (dense).
+ * Per tile: scale = max(amax, 1e-10) * fp32(1/448); code = RNE_e4m3(clamp(x / scale, +-448)) -
+ * the rule of python/gaudi_kernels/block_fp8_oracle.py:27-28 applied to a square tile (the reference
+ * has no weight quantizer of its own).  native_half != 0 additionally applies the half-range map
+ * and stores 2*scale (block_fp8_oracle.py:31-35), in the same pass. */
+int bfp8_quant_block128_f32(const float* w, int64_t rows, int64_t cols, int64_t ld,
+                            uint8_t* codes, int64_t ld_codes, float* scales,
+                            int native_half, void* stream);
+
+/* 1x128 activation quantizer, bf16 [m, k] (row stride ldx) -> E4M3 codes [m, k] (row stride
+ * ld_codes) + fp32 scales addressed as scales[row * scale_stride_m + group * scale_stride_g].
+ * Replaces python/gaudi_kernels/block_fp8_oracle.py:25-28 (and :31-34 when native_half != 0); the
+ * Gaudi2 counterpart is gk_fp8_block_quant_bf16_v1 (csrc/tpc/block_fp8_framework/activation_native.c:9-29).
+ * A ragged last group (k % 128 != 0) is treated as zero-padded.  status_dev may be NULL; otherwise
+ * NONFINITE_INPUT is raised for an inf/NaN activation (the check of block_fp8_oracle.py:22). */
+int bfp8_quant_act_1x128_bf16(const uint16_t* x, int64_t m, int64_t k, int64_t ldx,
+                              uint8_t* codes, int64_t ld_codes,
+                              float* scales, int64_t scale_stride_m, int64_t scale_stride_g,
+                              int native_half, uint32_t* status_dev, void* stream);
+
+/* value(code) * block scale -> fp32 or bf16 [rows, cols].  value() is the E4M3 decode of
+ * tests/test_fp8_codec.py:8-12; the Gaudi2 counterpart of the scaling is
+ * gk_fp8_dequant_weight_fp16_1k_v1 (csrc/tpc/block_fp8_framework/dequant_weight_fp16_1k.c:5-30).
+ * scales is [ceil(rows/128), ceil(cols/128)] dense.  out_dtype: BFP8_OUT_F32 or BFP8_OUT_BF16;
+ * ld_out in elements of that type. */
+int bfp8_decode_block128(const uint8_t* codes, int64_t rows, int64_t cols, int64_t ld,
+                         const float* scales, void* out, int out_dtype, int64_t ld_out,
+                         void* stream);
+
+/* Block-scaled E4M3 GEMM:
+ *   out[i, j] = sum_g a_scales[g, i] * w_scales[j / 128, g] * sum_{t < 128} a(i, 128 g + t) * w(j, 128 g + t) (+ bias[j])
+ * Replaces the numerical contract of gaudi_kernels.block_fp8_oracle.reference
+ * (python/gaudi_kernels/block_fp8_oracle.py:38-46) for operands that are already quantized; on Gaudi2 the
+ * same contraction is an MME batched GEMM followed by gk_fp8_block_reduce_bf16_v1
+ * (csrc/tpc/block_fp8_framework/reduce_bias.c:13-61).
+ *   a_codes  uint8 E4M3 [m, k], row stride lda bytes (lda % 16 == 0, base 16-byte aligned)
+ *   a_scales fp32, element (g, i) at a_scales[g * ldsa + i]   (group-major, ldsa >= m)
+ *   w_codes  uint8 E4M3 [n, k], row stride ldw bytes (ldw % 16 == 0, base 16-byte aligned)
+ *   w_scales fp32 [ceil(n/128), ceil(k/128)] dense
+ *   bias     fp32 [n] or NULL
+ *   out      fp32 or bf16 [m, n], row stride ldo elements (bf16: ldo % 8 == 0 and base 16-byte aligned)
+ * Codes are consumed as OCP E4M3 by the tensor cores; Gaudi2 half-range codes (magnitude <= 0x76)
+ * mean the same values under that format.  Each 128-wide block dot product is accumulated by the
+ * tensor core in fp32 (TMEM); the promotion across K blocks is an fp32 FMA chain in g order.
+ * workspace: bfp8_gemm_block128_workspace_bytes(m, n, k) bytes, 256-byte aligned (may be NULL if 0).
+ * status |= WAIT_TIMEOUT if an internal barrier wait gave up (output is then undefined). */
+size_t bfp8_gemm_block128_workspace_bytes(int64_t m, int64_t n, int64_t k);
+int bfp8_gemm_block128(const uint8_t* a_codes, int64_t lda, const float* a_scales, int64_t ldsa,
+                       const uint8_t* w_codes, int64_t ldw, const float* w_scales,
+                       const float* bias, void* out, int out_dtype, int64_t ldo,
+                       int64_t m, int64_t n, int64_t k,
+                       void* workspace, size_t workspace_bytes,
+                       uint32_t* status_dev, void* stream);
+
+
+/* Same as bfp8_gemm_block128 with tuning / diagnostic knobs (0 = default for each):
+ *   schedule           0 automatic; 1 force the large-tile schedule; 2 force the small-M schedule
+ *   max_ctas           upper bound on the persistent grid
+ *   wait_limit_cycles  SM-clock budget of every internal barrier wait before WAIT_TIMEOUT is raised
+ * The reference has no counterpart; its launch geometry is fixed per GUID in
+ * csrc/host/generic_fp8_glue.hpp:95-98,125-130. */
+int bfp8_gemm_block128_ex(const uint8_t* a_codes, int64_t lda, const float* a_scales, int64_t ldsa,
+                          const uint8_t* w_codes, int64_t ldw, const float* w_scales,
+                          const float* bias, void* out, int out_dtype, int64_t ldo,
+                          int64_t m, int64_t n, int64_t k,
+                          void* workspace, size_t workspace_bytes,
+                          uint32_t* status_dev, void* stream,
+                          int schedule, int max_ctas, int64_t wait_limit_cycles);
+
+#ifdef __cplusplus
+}
+#endif
+#endif  /* BFP8_H_ */

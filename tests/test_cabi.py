@@ -1,0 +1,90 @@
+"""Host-only checks of the C-ABI library: it builds, loads without a GPU, and exports what the header declares."""
+
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from gaudi_kernels_b200 import _lib, build
+    build.build()
+    return _lib.load()
+
+
+def _declared_symbols():
+    names = set()
+    for fn in os.listdir(os.path.join(ROOT, "include")):
+        if fn.endswith(".h"):
+            text = open(os.path.join(ROOT, "include", fn)).read()
+            text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+            names |= set(re.findall(r"\b(bfp8_\w+)\s*\(", text))
+    return names
+
+
+def test_header_symbols_are_exported(lib):
+    from gaudi_kernels_b200 import _lib
+    declared = _declared_symbols()
+    assert len(declared) >= 9
+    raw = ctypes.CDLL(_lib.LIB_PATH)
+    for name in declared:
+        assert hasattr(raw, name), name
+    assert declared == set(_lib.SIGNATURES), declared ^ set(_lib.SIGNATURES)
+
+
+def test_version_and_error_strings(lib):
+    assert lib.bfp8_version() >= 1
+    assert lib.bfp8_error_string(0) == b"ok"
+    for code in range(-6, 0):
+        assert lib.bfp8_error_string(code) not in (b"ok", b"unknown error")
+    assert lib.bfp8_gemm_block128_workspace_bytes(8192, 14336, 4096) >= 0
+
+
+def test_host_side_argument_checks_launch_nothing(lib):
+    # all of these are rejected before any CUDA call, so they are safe without a device
+    assert lib.bfp8_reencode_half(None, None, 16, None, None, 0, None, None, None) == -1
+    one = ctypes.c_uint64(0)
+    p = ctypes.addressof(one)
+    assert lib.bfp8_reencode_half(p, p, 0, None, None, 0, p, p, None) == -3
+    assert lib.bfp8_quant_block128_f32(p, 0, 4, 4, p, 4, p, 0, None) == -3
+    assert lib.bfp8_quant_act_1x128_bf16(p, 1, 128, 64, p, 128, p, 1, 1, 0, None, None) == -3
+    assert lib.bfp8_decode_block128(p, 4, 4, 4, p, p, 7, 4, None) == -3
+    # GEMM: misaligned leading dimension, then bad shape
+    a = 4096
+    assert lib.bfp8_gemm_block128(a, 130, a, 8, a, 136, a, None, a, 1, 16, 8, 16, 130, None, 0, a, None) == -2
+    assert lib.bfp8_gemm_block128(a, 128, a, 8, a, 128, a, None, a, 1, 16, 0, 16, 128, None, 0, a, None) == -3
+    assert lib.bfp8_gemm_block128(None, 128, a, 8, a, 128, a, None, a, 1, 16, 8, 16, 128, None, 0, a, None) == -1
+
+
+def test_python_wrappers_validate_like_the_reference():
+    import torch
+    import gaudi_kernels_b200 as gk
+    w = torch.tensor([[0x08, 0x10, 0x78], [0x03, 0x7E, 0x80]], dtype=torch.uint8).view(torch.float8_e4m3fn)
+    s = torch.tensor([[0.25, 0.5]], dtype=torch.float32)
+    with pytest.raises(ValueError):
+        gk.reencode_e4m3fn_half(w.t(), s)                       # non-contiguous
+    with pytest.raises(ValueError):
+        gk.reencode_e4m3fn_half(w, s.to(torch.float64))         # wrong scale dtype
+    with pytest.raises(ValueError):
+        gk.reencode_e4m3fn_half(w.view(torch.uint8), s)         # wrong weight dtype
+    x = torch.zeros((1, 256), dtype=torch.bfloat16)
+    wt = torch.zeros((128, 256), dtype=torch.uint8).view(torch.float8_e4m3fn)
+    with pytest.raises(ValueError, match="scale grid"):
+        gk.reference(x, wt, torch.ones((1, 1)))
+    with pytest.raises(ValueError):
+        gk.reference(x.float(), wt, torch.ones((1, 2)))
+
+
+def test_no_silent_fallback_without_a_gpu():
+    import torch
+    import gaudi_kernels_b200 as gk
+    from gaudi_kernels_b200._lib import Bfp8Error
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    w = torch.zeros(16, dtype=torch.uint8).view(torch.float8_e4m3fn)
+    with pytest.raises(Bfp8Error):
+        gk.reencode_e4m3fn_half(w, torch.ones(1))

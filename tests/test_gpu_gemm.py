@@ -1,0 +1,166 @@
+"""GPU parity of the block-scaled GEMM (through the C ABI) against the CPU oracle.
+
+Gate (relative tolerance 1e-2): max |y_kernel - y_oracle| / rms(y_oracle) <= 1e-2 on the values
+before bf16 rounding (fp32 kernel output against the oracle's FP64 sum).  The bf16 output must equal
+the round-to-nearest-even of the kernel's own fp32 output, differ from the oracle's bf16 by at most
+one bf16 ulp per element, and pass the reference's device gate: per-row relative L2 <= 0.01.
+"""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import block_fp8_ref, fp8_codec_ref
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-2
+
+
+@pytest.fixture(scope="module")
+def gk():
+    import gaudi_kernels_b200 as g
+    from gaudi_kernels_b200 import _lib
+    _lib.load()
+    return g
+
+
+def _case_tensors(c):
+    x = torch.from_numpy(c["x_bf16_bits"]).view(torch.bfloat16)
+    w = torch.from_numpy(c["w_codes"]).view(torch.float8_e4m3fn)
+    s = torch.from_numpy(c["w_scales"])
+    b = None if c["bias"] is None else torch.from_numpy(c["bias"])
+    return x, w, s, b
+
+
+def _ulp_distance_bf16(a, b):
+    def key(t):
+        i = t.view(torch.int16).to(torch.int32)
+        return torch.where(i < 0, -(i & 0x7FFF), i)
+    return (key(a) - key(b)).abs()
+
+
+def check_against_oracle(gk, x, w, s, b, half, label, y64=None, ybf=None):
+    if y64 is None:
+        y64, ybf = block_fp8_ref.reference_rows(x, w, s, native_half=half, bias=b)
+    xd, wd, sd = x.cuda(), w.cuda(), s.cuda()
+    bd = None if b is None else b.cuda()
+    got32 = gk.reference(xd, wd, sd, native_half=half, bias=bd, out_dtype=torch.float32).cpu()
+    got16 = gk.reference(xd, wd, sd, native_half=half, bias=bd).cpu()
+    assert got16.dtype == torch.bfloat16 and got16.shape == ybf.shape
+    rms = float(y64.pow(2).mean().sqrt())
+    if rms == 0.0:
+        assert not bool(got32.any()) and not bool(got16.any())
+        return 0.0
+    metric = float((got32.double() - y64).abs().max()) / rms
+    assert metric <= TOL, (label, metric)
+    assert torch.equal(got16, got32.to(torch.bfloat16)), label              # same accumulator, RNE
+    assert int(_ulp_distance_bf16(got16, ybf).max()) <= 1, label
+    num = (got16.double() - ybf.double()).pow(2).sum(1).sqrt()
+    den = ybf.double().pow(2).sum(1).sqrt()
+    live = den > 0
+    assert bool((num[~live] == 0).all()), label                             # identically-zero rows stay zero
+    assert bool((num[live] / den[live] <= 0.01).all()), label
+    return metric
+
+
+@pytest.mark.parametrize("half", [False, True])
+def test_gemm_matches_reference_fixtures(gk, golden_gemm, gemm_cases, half):
+    for name, c in gemm_cases.items():
+        x, w, s, b = _case_tensors(c)
+        want = torch.from_numpy(golden_gemm[f"{name}.y_bits.half{int(half)}"]).view(torch.bfloat16)
+        y64, ybf = block_fp8_ref.reference_rows(x, w, s, native_half=half, bias=b)
+        assert torch.equal(ybf, want)
+        check_against_oracle(gk, x, w, s, b, half, name, y64, ybf)
+
+
+def test_host_tensors_round_trip(gk, gemm_cases):
+    # the call a CPU user of the reference makes: host tensors in, host bf16 out
+    x, w, s, b = _case_tensors(gemm_cases["small_bias"])
+    y = gk.reference(x, w, s, native_half=True, bias=b)
+    assert y.device.type == "cpu" and y.dtype == torch.bfloat16
+    assert torch.equal(y, gk.reference(x.cuda(), w.cuda(), s.cuda(), native_half=True, bias=b.cuda()).cpu())
+
+
+def test_reference_rejects_nonfinite(gk, gemm_cases):
+    x, w, s, b = _case_tensors(gemm_cases["small_bias"])
+    bad = x.clone()
+    bad[2, 17] = float("inf")
+    with pytest.raises(ValueError):
+        gk.reference(bad.cuda(), w.cuda(), s.cuda(), native_half=True)
+    wb = w.view(torch.uint8).clone()
+    wb[5, 5] = 0x7F
+    for half in (False, True):
+        with pytest.raises(ValueError):
+            gk.reference(x.cuda(), wb.view(torch.float8_e4m3fn).cuda(), s.cuda(), native_half=half)
+    sb = s.clone()
+    sb[0, 0] = -1.0
+    with pytest.raises(ValueError):
+        gk.reference(x.cuda(), w.cuda(), sb.cuda(), native_half=True)
+
+
+def _random_problem(m, k, n, seed, bias=False):
+    rng = np.random.default_rng(seed)
+    x = torch.from_numpy(rng.standard_normal((m, k), dtype=np.float32)).to(torch.bfloat16)
+    wf = rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02)
+    codes, scales = fp8_codec_ref.quantize_block128(wf)
+    b = torch.from_numpy(rng.standard_normal(n, dtype=np.float32) * np.float32(0.1)) if bias else None
+    return x, torch.from_numpy(codes).view(torch.float8_e4m3fn), torch.from_numpy(scales), b
+
+
+@pytest.mark.parametrize("m,k,n", [(1, 128, 128), (1, 4096, 512), (8, 1024, 256), (32, 512, 384), (64, 2048, 1024),
+                                   (129, 256, 257), (130, 384, 520), (300, 1152, 640), (512, 640, 1032)])
+def test_gemm_shapes(gk, m, k, n):
+    x, w, s, b = _random_problem(m, k, n, seed=m * 31 + n, bias=(m % 2 == 0))
+    check_against_oracle(gk, x, w, s, b, True, (m, k, n))
+
+
+def test_gemm_output_tail_is_untouched(gk):
+    # sentinel columns right of N and rows below M must survive (out-of-bounds write check)
+    m, k, n = 70, 256, 200
+    x, w, s, _ = _random_problem(m, k, n, seed=5)
+    a_codes, a_scales = gk.quantize_act_1x128(x.cuda(), native_half=True)
+    wc, ws = gk.prepare_weight(w, s, native_half=True)
+    for dtype in (torch.bfloat16, torch.float32):
+        buf = torch.full((m + 3, n + 24), 0.5, dtype=dtype, device="cuda")
+        out = buf[:m, :n]
+        gk.gemm_block_fp8(a_codes, a_scales, wc, ws, out=out, out_dtype=dtype)
+        assert bool((buf[m:, :] == 0.5).all()) and bool((buf[:, n:] == 0.5).all())
+        y64, _ = block_fp8_ref.reference_rows(x, w, s, native_half=True)
+        assert float((out.double().cpu() - y64).abs().max()) / float(y64.pow(2).mean().sqrt()) <= TOL
+
+
+def test_gemm_many_tiles_persistent_loop(gk):
+    # more tiles than SMs, and a grid capped far below the tile count: every CTA walks several tiles
+    m, k, n = 1024, 512, 2048
+    x, w, s, b = _random_problem(m, k, n, seed=11, bias=True)
+    y64, ybf = block_fp8_ref.reference_rows(x, w, s, native_half=True, bias=b)
+    a_codes, a_scales = gk.quantize_act_1x128(x.cuda(), native_half=True)
+    wc, ws = gk.prepare_weight(w, s, native_half=True)
+    rms = float(y64.pow(2).mean().sqrt())
+    for cap in (0, 5, 1):
+        out = gk.gemm_block_fp8(a_codes, a_scales, wc, ws, bias=b.cuda(), out_dtype=torch.float32, max_ctas=cap)
+        assert float((out.double().cpu() - y64).abs().max()) / rms <= TOL, cap
+
+
+def test_gemm_prefill_shape_row_sample(gk):
+    # the prefill configuration M=8192, K=4096, N=14336 at full size, checked on a seeded sample of rows
+    m, k, n = 8192, 4096, 14336
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn((m, k), generator=g).to(torch.bfloat16)
+    wf = (torch.randn((n, k), generator=g) * 0.02).cuda()
+    w_ocp, s_ocp = gk.quantize_block128(wf)
+    del wf
+    wc, ws = gk.prepare_weight(w_ocp, s_ocp, native_half=True)
+    a_codes, a_scales = gk.quantize_act_1x128(x.cuda(), native_half=True)
+    out16 = gk.gemm_block_fp8(a_codes, a_scales, wc, ws)
+    out32 = gk.gemm_block_fp8(a_codes, a_scales, wc, ws, out_dtype=torch.float32)
+    assert torch.equal(out16, out32.to(torch.bfloat16))
+    rows = torch.randperm(m, generator=g)[:48].sort().values
+    y64, ybf = block_fp8_ref.reference_rows(x[rows], w_ocp.cpu(), s_ocp.cpu(), native_half=True)
+    rms = float(y64.pow(2).mean().sqrt())
+    assert float((out32[rows.cuda()].double().cpu() - y64).abs().max()) / rms <= TOL
+    assert int(_ulp_distance_bf16(out16[rows.cuda()].cpu(), ybf).max()) <= 1
+    # linearity in the weight scales (size-independent property): doubling every scale doubles the output exactly
+    out_2x = gk.gemm_block_fp8(a_codes, a_scales, wc, ws * 2, out_dtype=torch.float32)
+    assert torch.equal(out_2x, out32 * 2)
