@@ -19,6 +19,20 @@ import torch
 from . import _lib
 from .fp8_codec import BLOCK, _device_for, _read_status, _status_buffer, _stream_ptr, quantize_act_1x128
 
+# Zero-initialised scratch per (device, stream).  The small-M schedule keeps per-tile arrival counters
+# there and returns them to zero, so one buffer serves every call issued on that stream.
+_workspaces = {}
+
+
+def _workspace(dev, nbytes):
+    key = (dev.index, _stream_ptr())
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.zeros(max(nbytes, 1), dtype=torch.uint8, device=dev)
+        _workspaces[key] = ws
+    return ws
+
+
 _WAIT_TIMEOUT_MSG = "a bounded wait inside the GEMM kernel expired (BFP8_STATUS_WAIT_TIMEOUT); output is invalid"
 
 
@@ -85,7 +99,7 @@ def gemm_block_fp8(a_codes, a_scales, w_codes, w_scales, bias=None, out=None, ou
                 raise ValueError("out must be [M, N] of out_dtype with unit column stride on the operand device")
             ldo = out.stride(0)
         ws_bytes = lib.bfp8_gemm_block128_workspace_bytes(m, n, k)
-        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev) if ws_bytes else None
+        ws = _workspace(dev, ws_bytes) if ws_bytes else None
         st = _status_buffer(dev)
         rc = lib.bfp8_gemm_block128_ex(
             a_codes.data_ptr(), lda, sa.data_ptr(), ldsa, w_codes.data_ptr(), ldw, w_scales.data_ptr(),
@@ -95,6 +109,7 @@ def gemm_block_fp8(a_codes, a_scales, w_codes, w_scales, bias=None, out=None, ou
             schedule, max_ctas, wait_limit_cycles)
         _lib.check(rc, "bfp8_gemm_block128")
         if check and _read_status(st)[1] & _lib.STATUS_WAIT_TIMEOUT:
+            _workspaces.clear()            # counters may have been left non-zero
             raise _lib.Bfp8Error(_WAIT_TIMEOUT_MSG)
     return out
 
@@ -113,11 +128,12 @@ def prepare_weight(weight, scales, native_half=True):
     return weight, scales
 
 
-def reference(x, weight, scales, *, native_half=False, bias=None, out_dtype=torch.bfloat16):
+def reference(x, weight, scales, *, native_half=False, bias=None, out_dtype=torch.bfloat16, out=None):
     """Drop-in for gaudi_kernels.block_fp8_oracle.reference, computed on the GPU.
 
     x bf16 [M, K]; weight float8_e4m3fn [N, K] (original OCP codes); scales fp32 [ceil(N/128), ceil(K/128)].
-    Host tensors are copied to the current CUDA device and the result is returned on the host.
+    Host tensors are copied to the current CUDA device and the result is returned on the host
+    (into `out` when given - a pinned [M, N] tensor makes that copy asynchronous up to the final wait).
     """
     if (not isinstance(x, torch.Tensor) or not isinstance(weight, torch.Tensor) or not isinstance(scales, torch.Tensor)
             or x.dtype != torch.bfloat16 or weight.dtype != torch.float8_e4m3fn
@@ -156,10 +172,18 @@ def reference(x, weight, scales, *, native_half=False, bias=None, out_dtype=torc
                                            a_scales.data_ptr(), 1, m, int(bool(native_half)),
                                            st.data_ptr() + 8, _stream_ptr())
         _lib.check(rc, "bfp8_quant_act_1x128_bf16")
-        y = gemm_block_fp8(a_codes, a_scales.t(), enc, sw, bias=bias, out_dtype=out_dtype, check=False)
-        status = _read_status(st)[1]
+        dev_out = out if (out is not None and out.device.type == "cuda") else None
+        y = gemm_block_fp8(a_codes, a_scales.t(), enc, sw, bias=bias, out=dev_out, out_dtype=out_dtype, check=False)
+        if on_host:
+            if out is None:
+                out = torch.empty(y.shape, dtype=y.dtype)
+            elif tuple(out.shape) != tuple(y.shape) or out.dtype != y.dtype:
+                raise ValueError("out must be [M, N] of the output dtype")
+            out.copy_(y, non_blocking=True)
+            y = out
+        status = _read_status(st)[1]               # synchronises: also completes the copy above
         if finite is not None and not bool(finite):
             status |= _lib.STATUS_NONFINITE_CODE
         if status & (_lib.STATUS_NONFINITE_CODE | _lib.STATUS_BAD_SCALE | _lib.STATUS_NONFINITE_INPUT):
             raise ValueError("finite original inputs required")
-    return y.cpu() if on_host else y
+    return y

@@ -27,6 +27,18 @@ inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_
 // Number of SMs of the current device (cached per device id).
 int sm_count();
 
+// Raise a kernel's dynamic shared-memory limit once per device (the attribute is per device context).
+template <typename Kernel>
+inline int ensure_smem_limit(Kernel kernel, int bytes, bool (&done)[64]) {
+  int dev = 0;
+  BFP8_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64 || !done[dev]) {
+    BFP8_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+    if (dev >= 0 && dev < 64) done[dev] = true;
+  }
+  return BFP8_OK;
+}
+
 // ---- E4M3 byte arithmetic -----------------------------------------------------------------
 
 // Half of four packed OCP E4M3FN codes, round-to-nearest-even, in the Gaudi2 encoding

@@ -6,6 +6,12 @@ int launch_gemm_large(const uint8_t* a_codes, int64_t lda, const float* a_scales
                       const uint8_t* w_codes, int64_t ldw, const float* w_scales, const float* bias, void* out,
                       int out_dtype, int64_t ldo, int64_t m, int64_t n, int64_t k, uint32_t* status_dev,
                       long long wait_limit, int max_ctas, cudaStream_t st);
+int launch_gemm_smallm(const uint8_t* a_codes, int64_t lda, const float* a_scales, int64_t ldsa,
+                       const uint8_t* w_codes, int64_t ldw, const float* w_scales, const float* bias, void* out,
+                       int out_dtype, int64_t ldo, int64_t m, int64_t n, int64_t k, void* workspace,
+                       uint32_t* status_dev, long long wait_limit, int max_ctas, cudaStream_t st);
+size_t smallm_workspace_bytes(int64_t m, int64_t n, int max_ctas);
+bool smallm_supported(int64_t n);
 }
 
 using namespace bfp8;
@@ -14,11 +20,15 @@ namespace {
 // About one second at B200 clocks: far beyond any legitimate wait, short enough that a broken
 // launch returns with BFP8_STATUS_WAIT_TIMEOUT instead of hanging the device.
 constexpr long long kDefaultWaitLimit = 2000000000LL;
+constexpr int64_t kSmallMRows = 128;     // up to this many activation rows the weight-streaming schedule runs
+constexpr int kMaxCtas = 256;            // workspace is sized for this many CTAs, whatever the device has
 }
 
 extern "C" size_t bfp8_gemm_block128_workspace_bytes(int64_t m, int64_t n, int64_t k) {
-  (void)m; (void)n; (void)k;
-  return 0;
+  (void)k;
+  if (m <= 0 || n <= 0) return 0;
+  // Sized for the small-M schedule whenever it could be selected (automatically or by `schedule`).
+  return (m <= kSmallMRows && smallm_supported(n)) ? smallm_workspace_bytes(m, n, kMaxCtas) : 0;
 }
 
 extern "C" int bfp8_gemm_block128_ex(const uint8_t* a_codes, int64_t lda, const float* a_scales, int64_t ldsa,
@@ -27,7 +37,6 @@ extern "C" int bfp8_gemm_block128_ex(const uint8_t* a_codes, int64_t lda, const 
                                      int64_t m, int64_t n, int64_t k,
                                      void* workspace, size_t workspace_bytes, uint32_t* status_dev, void* stream,
                                      int schedule, int max_ctas, int64_t wait_limit_cycles) {
-  (void)schedule;
   if (!a_codes || !a_scales || !w_codes || !w_scales || !out || !status_dev) return BFP8_ERR_NULL;
   if (m <= 0 || n <= 0 || k <= 0 || m > (1 << 30) || n > (1 << 30) || k > (1 << 30)) return BFP8_ERR_SHAPE;
   if (lda < k || ldw < k || ldo < n || ldsa < m) return BFP8_ERR_SHAPE;
@@ -37,11 +46,20 @@ extern "C" int bfp8_gemm_block128_ex(const uint8_t* a_codes, int64_t lda, const 
   if (bias && !aligned(bias, 4)) return BFP8_ERR_ALIGN;
   if (out_dtype == BFP8_OUT_BF16 && (!aligned(out, 16) || ldo % 8 != 0)) return BFP8_ERR_ALIGN;
   if (out_dtype == BFP8_OUT_F32 && !aligned(out, 4)) return BFP8_ERR_ALIGN;
-  const size_t need = bfp8_gemm_block128_workspace_bytes(m, n, k);
-  if (need > 0 && (!workspace || workspace_bytes < need)) return BFP8_ERR_WORKSPACE;
+  if (schedule < 0 || schedule > 2 || (schedule == 2 && (m > kSmallMRows || !smallm_supported(n)))) return BFP8_ERR_SHAPE;
+  const bool small = schedule == 2 || (schedule == 0 && m <= kSmallMRows && smallm_supported(n));
   const long long limit = wait_limit_cycles > 0 ? wait_limit_cycles : kDefaultWaitLimit;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (small) {
+    const size_t need = bfp8_gemm_block128_workspace_bytes(m, n, k);
+    if (!workspace || workspace_bytes < need) return BFP8_ERR_WORKSPACE;
+    if (!aligned(workspace, 256)) return BFP8_ERR_ALIGN;
+    if (sm_count() > kMaxCtas) return BFP8_ERR_UNSUPPORTED;
+    return launch_gemm_smallm(a_codes, lda, a_scales, ldsa, w_codes, ldw, w_scales, bias, out, out_dtype, ldo,
+                              m, n, k, workspace, status_dev, limit, max_ctas, st);
+  }
   return launch_gemm_large(a_codes, lda, a_scales, ldsa, w_codes, ldw, w_scales, bias, out, out_dtype, ldo, m, n, k,
-                           status_dev, limit, max_ctas, static_cast<cudaStream_t>(stream));
+                           status_dev, limit, max_ctas, st);
 }
 
 extern "C" int bfp8_gemm_block128(const uint8_t* a_codes, int64_t lda, const float* a_scales, int64_t ldsa,

@@ -1,0 +1,392 @@
+// Small-M ("decode bucket") schedule of the block-scaled E4M3 GEMM for sm_100a.
+//
+// With at most 128 activation rows the GEMM is a single pass over the weight matrix and is bound
+// by HBM, so the schedule is built around streaming W exactly once at full bandwidth:
+//   * operands are swapped: 128 weight rows are the MMA's M dimension (TMEM lanes) and the padded
+//     activation rows (16 / 32 / 64 / 128) its N dimension, so no tensor-core work is wasted on padding W;
+//   * the work is cut into units of (128 weight rows) x (one 128-wide K block) = 16 KB of W, and the
+//     unit list - tile-major, K-block-minor - is split evenly over the CTAs (stream-K), so every SM
+//     streams the same number of bytes whatever N and K are;
+//   * a CTA that finishes only part of a tile's K range writes its fp32 partial to the workspace; the
+//     last CTA to arrive at a tile (per-tile counter) adds the partials in CTA order - a fixed order,
+//     so results do not depend on timing - applies the bias and stores the tile.  Counters are
+//     returned to zero, so a zero-initialised workspace stays reusable.
+// Each K block is accumulated from zero into one of four small TMEM buffers and folded into register
+// accumulators with its scale product sa[g, i] * sw[j/128, g], as in the large-tile schedule.
+//
+// Warp roles (224 threads): warps 0-3 epilogue (thread = weight row), warp 4 TMA producer, warp 5
+// TMEM owner and MMA issuer, warp 6 scale loader: it fetches the scale products of the units ahead
+// (global-memory latency is far longer than a unit's 16 KB of HBM time) and parks them in a small
+// shared-memory ring next to the TMEM buffers.  All barrier waits are bounded.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace bfp8 {
+
+namespace {
+
+constexpr int BN = 128;            // weight rows per tile = one scale block
+constexpr int BK = 128;
+constexpr int kEpiWarps = 4;
+constexpr int kThreads = (kEpiWarps + 3) * 32;
+constexpr int kScaleAhead = 4;     // units whose scales are in flight in the loader's registers
+constexpr int kAccBufs = 4;
+constexpr int kWBytes = BN * BK;   // 16 KB of W per unit
+constexpr int kMaxStages = 10;
+constexpr int kSmemBudget = 200 * 1024;
+
+template <int MP>
+struct Cfg {
+  static constexpr int kABytes = MP * BK;
+  static constexpr int kStageBytes = kWBytes + kABytes;
+  static constexpr int kStages = (kSmemBudget / kStageBytes) < kMaxStages ? (kSmemBudget / kStageBytes) : kMaxStages;
+  static constexpr int kTmemCols = (kAccBufs * MP) < 32 ? 32 : (kAccBufs * MP);
+};
+
+struct SmemTail {
+  uint64_t full[kMaxStages];
+  uint64_t empty[kMaxStages];
+  uint64_t tmem_full[kAccBufs];
+  uint64_t tmem_empty[kAccBufs];
+  uint64_t scale_full[kAccBufs];
+  float scale[kAccBufs][128];        // sa[g, 0..MP) * sw[tile, g] of the unit in each TMEM buffer
+  uint32_t tmem_base;
+  uint32_t abort_flag;
+  uint32_t last_flag;
+};
+
+struct Params {
+  const float* a_scales;   // [G, ldsa]
+  const float* w_scales;   // [NB, G]
+  const float* bias;
+  void* out;
+  uint32_t* counters;      // [tiles], zero on entry, zero on exit
+  float* partials;         // [ctas][2][MP][128]
+  int64_t ldsa, ldo;
+  int m, n, groups, tiles;
+  int out_bf16;
+  long long total_units;
+  long long wait_limit;
+  uint32_t* status;
+};
+
+// First unit of CTA c when `total` units are split over `parts` CTAs.
+__host__ __device__ inline long long first_unit(long long c, long long total, long long parts) {
+  return c * total / parts;
+}
+// The CTA whose range contains unit u.
+__host__ __device__ inline int cta_of_unit(long long u, long long total, long long parts) {
+  return static_cast<int>(((u + 1) * parts - 1) / total);
+}
+
+template <int MP>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a,
+                   const Params p) {
+  using C = Cfg<MP>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
+  SmemTail* tail = reinterpret_cast<SmemTail*>(smem + C::kStages * C::kStageBytes);
+  volatile uint32_t* abort_flag = &tail->abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int G = p.groups;
+  const long long parts = gridDim.x;
+  const long long u0 = first_unit(blockIdx.x, p.total_units, parts);
+  const long long u1 = first_unit(blockIdx.x + 1, p.total_units, parts);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::kStages; ++s) {
+      ptx::mbar_init(ptx::smem_u32(&tail->full[s]), 1);
+      ptx::mbar_init(ptx::smem_u32(&tail->empty[s]), 1);
+    }
+    for (int b = 0; b < kAccBufs; ++b) {
+      ptx::mbar_init(ptx::smem_u32(&tail->tmem_full[b]), 1);
+      ptx::mbar_init(ptx::smem_u32(&tail->tmem_empty[b]), kEpiWarps);
+      ptx::mbar_init(ptx::smem_u32(&tail->scale_full[b]), 1);
+    }
+    tail->abort_flag = 0;
+    ptx::fence_mbar_init();
+  }
+  if (warp == kEpiWarps + 1) {
+    ptx::tmem_alloc(ptx::smem_u32(&tail->tmem_base), C::kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  if (warp == kEpiWarps && lane == 0) {
+    ptx::prefetch_tensormap(&tmap_w);
+    ptx::prefetch_tensormap(&tmap_a);
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = tail->tmem_base;
+
+  if (warp == kEpiWarps) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      for (long long u = u0; u < u1; ++u) {
+        const int tile = static_cast<int>(u / G), g = static_cast<int>(u % G);
+        if (!ptx::mbar_wait(ptx::smem_u32(&tail->empty[stage]), phase ^ 1u, abort_flag, p.wait_limit)) break;
+        const uint32_t full = ptx::smem_u32(&tail->full[stage]);
+        const uint32_t w_dst = smem_base + stage * C::kStageBytes;
+        ptx::mbar_arrive_expect_tx(full, C::kStageBytes);
+        ptx::tma_load_2d(w_dst, &tmap_w, full, g * BK, tile * BN);
+        ptx::tma_load_2d(w_dst + kWBytes, &tmap_a, full, g * BK, 0);
+        if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+      }
+    }
+  } else if (warp == kEpiWarps + 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = ptx::umma_idesc_e4m3(BN, MP);
+      uint32_t stage = 0, phase = 0, kb = 0;
+      for (long long u = u0; u < u1; ++u, ++kb) {
+        const uint32_t buf = kb % kAccBufs, acc_phase = (kb / kAccBufs) & 1u;
+        if (!ptx::mbar_wait(ptx::smem_u32(&tail->tmem_empty[buf]), acc_phase ^ 1u, abort_flag, p.wait_limit)) break;
+        if (!ptx::mbar_wait(ptx::smem_u32(&tail->full[stage]), phase, abort_flag, p.wait_limit)) break;
+        ptx::tc_fence_after_sync();
+        const uint32_t w_addr = smem_base + stage * C::kStageBytes;
+        const uint64_t w_desc = ptx::umma_desc_k128(w_addr);
+        const uint64_t a_desc = ptx::umma_desc_k128(w_addr + kWBytes);
+        const uint32_t d = tmem_base + buf * MP;
+#pragma unroll
+        for (int k4 = 0; k4 < BK / 32; ++k4)
+          ptx::umma_f8(d, w_desc + 2u * k4, a_desc + 2u * k4, idesc, k4 > 0);
+        ptx::umma_commit(ptx::smem_u32(&tail->empty[stage]));
+        ptx::umma_commit(ptx::smem_u32(&tail->tmem_full[buf]));
+        if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+      }
+    }
+  } else if (warp == kEpiWarps + 2) {
+    // ------------------------------------------------------------------ scale loader
+    constexpr int kPer = (MP + 31) / 32;                         // scale products per lane and unit
+    float v[kScaleAhead][kPer];
+    auto fetch = [&](long long u, float (&dst)[kPer]) {
+      const int tile = static_cast<int>(u / G), g = static_cast<int>(u % G);
+      const float sw = __ldg(p.w_scales + static_cast<int64_t>(tile) * G + g);
+      const float* sa = p.a_scales + static_cast<int64_t>(g) * p.ldsa;
+#pragma unroll
+      for (int q = 0; q < kPer; ++q) {
+        const int i = lane + 32 * q;
+        dst[q] = (i < p.m) ? __ldg(sa + i) * sw : 0.0f;
+      }
+    };
+#pragma unroll
+    for (int i = 0; i < kScaleAhead; ++i)
+      if (u0 + i < u1) fetch(u0 + i, v[i]);
+    uint32_t kb = 0;
+    bool ok = true;
+    for (long long base = u0; base < u1 && ok; base += kScaleAhead) {
+#pragma unroll
+      for (int i = 0; i < kScaleAhead; ++i) {
+        const long long u = base + i;
+        if (u < u1 && ok) {
+          const uint32_t buf = kb % kAccBufs, acc_phase = (kb / kAccBufs) & 1u;
+          ok = ptx::mbar_wait(ptx::smem_u32(&tail->tmem_empty[buf]), acc_phase ^ 1u, abort_flag, p.wait_limit);
+          if (ok) {
+#pragma unroll
+            for (int q = 0; q < kPer; ++q)
+              if (lane + 32 * q < MP) tail->scale[buf][lane + 32 * q] = v[i][q];
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&tail->scale_full[buf]));
+            if (u + kScaleAhead < u1) fetch(u + kScaleAhead, v[i]);
+            ++kb;
+          }
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue / promotion
+    const int wrow = warp * 32 + lane;                         // weight row inside the tile = TMEM lane
+    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    const int epi_tid = threadIdx.x;                           // 0..127
+    float acc[MP];
+#pragma unroll
+    for (int j = 0; j < MP; ++j) acc[j] = 0.0f;
+    uint32_t kb = 0;
+    long long seg_start = u0;
+    bool ok = true;
+    for (long long u = u0; u < u1 && ok; ++u, ++kb) {
+      const int tile = static_cast<int>(u / G), g = static_cast<int>(u % G);
+      const uint32_t buf = kb % kAccBufs, acc_phase = (kb / kAccBufs) & 1u;
+      ok = ptx::mbar_wait(ptx::smem_u32(&tail->tmem_full[buf]), acc_phase, abort_flag, p.wait_limit) &&
+           ptx::mbar_wait(ptx::smem_u32(&tail->scale_full[buf]), acc_phase, abort_flag, p.wait_limit);
+      if (!ok) break;
+      ptx::tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + lane_addr + buf * MP;
+      constexpr int kChunk = MP < 64 ? MP : 64;                  // columns fetched per TMEM round trip
+#pragma unroll
+      for (int h = 0; h < MP / kChunk; ++h) {
+        uint32_t r[kChunk / 16][16];
+#pragma unroll
+        for (int c = 0; c < kChunk / 16; ++c) ptx::tmem_ld16(taddr + h * kChunk + c * 16, r[c]);
+        float s[kChunk];
+#pragma unroll
+        for (int j = 0; j < kChunk; j += 4) {
+          const float4 t4 = *reinterpret_cast<const float4*>(&tail->scale[buf][h * kChunk + j]);
+          s[j] = t4.x; s[j + 1] = t4.y; s[j + 2] = t4.z; s[j + 3] = t4.w;
+        }
+        ptx::tmem_wait_ld16(r[0]);
+#pragma unroll
+        for (int c = 1; c < kChunk / 16; ++c) ptx::tmem_regs_ready16(r[c]);
+#pragma unroll
+        for (int c = 0; c < kChunk / 16; ++c)
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            acc[h * kChunk + c * 16 + j] = fmaf(__uint_as_float(r[c][j]), s[c * 16 + j], acc[h * kChunk + c * 16 + j]);
+      }
+      ptx::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&tail->tmem_empty[buf]));
+
+      if (g == G - 1 || u == u1 - 1) {
+        // ---- end of this CTA's segment of the tile
+        const long long tile_first = static_cast<long long>(tile) * G;
+        const int c_first = cta_of_unit(tile_first, p.total_units, parts);
+        const int c_last = cta_of_unit(tile_first + G - 1, p.total_units, parts);
+        const int col = tile * BN + wrow;
+        const bool whole = (seg_start == tile_first) && (g == G - 1);
+        bool do_store = whole;
+        if (!whole) {
+          // partial slot: 0 if this tile is the CTA's first, else 1
+          const int slot = (static_cast<long long>(tile) == u0 / G) ? 0 : 1;
+          float* dst = p.partials + (static_cast<int64_t>(blockIdx.x) * 2 + slot) * (MP * BN);
+#pragma unroll
+          for (int j = 0; j < MP; ++j) dst[j * BN + wrow] = acc[j];
+          __threadfence();
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (epi_tid == 0) {
+            const uint32_t prev = atomicAdd(p.counters + tile, 1u);
+            const uint32_t nseg = static_cast<uint32_t>(c_last - c_first + 1);
+            tail->last_flag = (prev == nseg - 1) ? 1u : 0u;
+            if (prev == nseg - 1) p.counters[tile] = 0;          // leave the workspace reusable
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          do_store = tail->last_flag != 0;
+          if (do_store) {
+            __threadfence();
+#pragma unroll
+            for (int j = 0; j < MP; ++j) acc[j] = 0.0f;
+            for (int c = c_first; c <= c_last; ++c) {              // fixed order: results are run-to-run identical
+              const int cslot = (static_cast<long long>(tile) == first_unit(c, p.total_units, parts) / G) ? 0 : 1;
+              const float* src = p.partials + (static_cast<int64_t>(c) * 2 + cslot) * (MP * BN);
+#pragma unroll
+              for (int j = 0; j < MP; ++j)
+                if (j < p.m) acc[j] += __ldcg(src + j * BN + wrow);
+            }
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");          // last_flag may be rewritten next segment
+        }
+        if (do_store && col < p.n) {
+          const float b = p.bias != nullptr ? __ldg(p.bias + col) : 0.0f;
+          if (p.out_bf16) {
+            uint16_t* o = reinterpret_cast<uint16_t*>(p.out) + col;
+#pragma unroll
+            for (int j = 0; j < MP; ++j)
+              if (j < p.m) o[static_cast<int64_t>(j) * p.ldo] = static_cast<uint16_t>(float_to_bf16_bits(acc[j] + b));
+          } else {
+            float* o = reinterpret_cast<float*>(p.out) + col;
+#pragma unroll
+            for (int j = 0; j < MP; ++j)
+              if (j < p.m) o[static_cast<int64_t>(j) * p.ldo] = acc[j] + b;
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < MP; ++j) acc[j] = 0.0f;
+        seg_start = u + 1;
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  if (warp == kEpiWarps + 1) ptx::tmem_dealloc(tmem_base, C::kTmemCols);
+  if (threadIdx.x == 0 && tail->abort_flag != 0) atomicOr(p.status, BFP8_STATUS_WAIT_TIMEOUT);
+}
+
+template <int MP>
+int launch(const CUtensorMap& tmap_w, const CUtensorMap& tmap_a, const Params& p, int grid, cudaStream_t st) {
+  using C = Cfg<MP>;
+  constexpr int smem = 1024 + C::kStages * C::kStageBytes + sizeof(SmemTail);
+  static bool done[64] = {};
+  const int rc = ensure_smem_limit(gemm_smallm_kernel<MP>, smem, done);
+  if (rc != BFP8_OK) return rc;
+  gemm_smallm_kernel<MP><<<grid, kThreads, smem, st>>>(tmap_w, tmap_a, p);
+  BFP8_CUDA_TRY(cudaGetLastError());
+  return BFP8_OK;
+}
+
+}  // namespace
+
+int make_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* base, uint64_t inner, uint64_t outer,
+                       uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer);
+
+int smallm_padded_rows(int64_t m) { return m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : 128; }
+
+// The arrival counters always occupy the first 64 KB of the workspace, whatever the shape, so a
+// workspace that is shared by calls of different shapes never sees partial sums where counters live.
+constexpr int64_t kMaxTiles = 16384;
+constexpr size_t kCounterBytes = kMaxTiles * sizeof(uint32_t);
+
+bool smallm_supported(int64_t n) { return (n + BN - 1) / BN <= kMaxTiles; }
+
+size_t smallm_workspace_bytes(int64_t m, int64_t n, int max_ctas) {
+  (void)n;
+  return kCounterBytes + static_cast<size_t>(max_ctas) * 2 * smallm_padded_rows(m) * BN * sizeof(float);
+}
+
+// Grid size: every CTA should stream the same number of 16 KB units.  When the tile count is close to
+// the SM count, one CTA per whole tile avoids every partial; otherwise the units are split evenly.
+int smallm_grid(int64_t tiles, int64_t groups, int sms) {
+  const long long units = tiles * groups;
+  if (units < sms) return static_cast<int>(units);
+  if (tiles <= sms && tiles * 4 >= static_cast<int64_t>(sms) * 3) return static_cast<int>(tiles);
+  return sms;
+}
+
+int launch_gemm_smallm(const uint8_t* a_codes, int64_t lda, const float* a_scales, int64_t ldsa,
+                       const uint8_t* w_codes, int64_t ldw, const float* w_scales, const float* bias, void* out,
+                       int out_dtype, int64_t ldo, int64_t m, int64_t n, int64_t k, void* workspace,
+                       uint32_t* status_dev, long long wait_limit, int max_ctas, cudaStream_t st) {
+  const int mp = smallm_padded_rows(m);
+  alignas(64) CUtensorMap tmap_w, tmap_a;
+  int rc = make_tensor_map_2d(&tmap_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, w_codes, k, n, ldw, BK, BN);
+  if (rc != BFP8_OK) return rc;
+  rc = make_tensor_map_2d(&tmap_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, a_codes, k, m, lda, BK, mp);
+  if (rc != BFP8_OK) return rc;
+  Params p;
+  p.a_scales = a_scales;
+  p.w_scales = w_scales;
+  p.bias = bias;
+  p.out = out;
+  p.ldsa = ldsa;
+  p.ldo = ldo;
+  p.m = static_cast<int>(m);
+  p.n = static_cast<int>(n);
+  p.groups = static_cast<int>((k + BK - 1) / BK);
+  p.tiles = static_cast<int>((n + BN - 1) / BN);
+  p.out_bf16 = out_dtype == BFP8_OUT_BF16;
+  p.total_units = static_cast<long long>(p.tiles) * p.groups;
+  p.wait_limit = wait_limit;
+  p.status = status_dev;
+  const int sms = sm_count();
+  int grid = smallm_grid(p.tiles, p.groups, sms);
+  if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
+  p.counters = reinterpret_cast<uint32_t*>(workspace);
+  p.partials = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + kCounterBytes);
+  switch (mp) {
+    case 16: return launch<16>(tmap_w, tmap_a, p, grid, st);
+    case 32: return launch<32>(tmap_w, tmap_a, p, grid, st);
+    case 64: return launch<64>(tmap_w, tmap_a, p, grid, st);
+    default: return launch<128>(tmap_w, tmap_a, p, grid, st);
+  }
+}
+
+}  // namespace bfp8

@@ -272,6 +272,8 @@ gemm_block128_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   if (threadIdx.x == 0 && tail->abort_flag != 0) atomicOr(p.status, BFP8_STATUS_WAIT_TIMEOUT);
 }
 
+}  // namespace
+
 // ---- host side ------------------------------------------------------------------------------------
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -291,15 +293,15 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
-int make_map_2d(CUtensorMap* map, CUtensorMapDataType dt, int elem_bytes, const void* base, uint64_t inner,
-                uint64_t outer, uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer) {
+// 2-D row-major tensor map with the 128-byte swizzle; box_inner * element size must be <= 128 bytes.
+int make_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* base, uint64_t inner, uint64_t outer,
+                       uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (fn == nullptr) return BFP8_ERR_CUDA;
   cuuint64_t dims[2] = {inner, outer};
   cuuint64_t strides[1] = {row_stride_bytes};
   cuuint32_t box[2] = {box_inner, box_outer};
   cuuint32_t estr[2] = {1, 1};
-  (void)elem_bytes;
   CUresult r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
@@ -309,20 +311,18 @@ int make_map_2d(CUtensorMap* map, CUtensorMapDataType dt, int elem_bytes, const 
   return BFP8_OK;
 }
 
-}  // namespace
-
 int launch_gemm_large(const uint8_t* a_codes, int64_t lda, const float* a_scales, int64_t ldsa,
                       const uint8_t* w_codes, int64_t ldw, const float* w_scales, const float* bias, void* out,
                       int out_dtype, int64_t ldo, int64_t m, int64_t n, int64_t k, uint32_t* status_dev,
                       long long wait_limit, int max_ctas, cudaStream_t st) {
   alignas(64) CUtensorMap tmap_a, tmap_w, tmap_out;
-  int rc = make_map_2d(&tmap_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a_codes, k, m, lda, BK, BM);
+  int rc = make_tensor_map_2d(&tmap_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, a_codes, k, m, lda, BK, BM);
   if (rc != BFP8_OK) return rc;
-  rc = make_map_2d(&tmap_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w_codes, k, n, ldw, BK, BN);
+  rc = make_tensor_map_2d(&tmap_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, w_codes, k, n, ldw, BK, BN);
   if (rc != BFP8_OK) return rc;
   const bool bf16 = out_dtype == BFP8_OUT_BF16;
   if (bf16) {
-    rc = make_map_2d(&tmap_out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, out, n, m, ldo * 2, 64, 32);
+    rc = make_tensor_map_2d(&tmap_out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, out, n, m, ldo * 2, 64, 32);
     if (rc != BFP8_OK) return rc;
   } else {
     tmap_out = tmap_a;   // unused on the fp32 path
@@ -347,7 +347,9 @@ int launch_gemm_large(const uint8_t* a_codes, int64_t lda, const float* a_scales
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   if (tiles < grid) grid = tiles;
   auto kern = bf16 ? gemm_block128_kernel<true> : gemm_block128_kernel<false>;
-  BFP8_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+  static bool done[2][64] = {};
+  rc = ensure_smem_limit(kern, kSmemBytes, done[bf16 ? 1 : 0]);
+  if (rc != BFP8_OK) return rc;
   kern<<<grid, kThreads, kSmemBytes, st>>>(tmap_a, tmap_w, tmap_out, p);
   BFP8_CUDA_TRY(cudaGetLastError());
   return BFP8_OK;

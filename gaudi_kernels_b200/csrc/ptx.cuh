@@ -169,5 +169,15 @@ __device__ __forceinline__ void tmem_wait_ld16(uint32_t (&r)[16]) {
                :: "memory");
 }
 
+// Compiler-only barrier for registers filled by an earlier tmem_ld16 whose completion was already
+// awaited through another register array: emits nothing, but keeps every use of `r` after it.
+__device__ __forceinline__ void tmem_regs_ready16(uint32_t (&r)[16]) {
+  asm volatile(""
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                 "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]),
+                 "+r"(r[15])
+               :: "memory");
+}
+
 }  // namespace ptx
 }  // namespace bfp8

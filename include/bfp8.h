@@ -105,6 +105,9 @@ int bfp8_decode_block128(const uint8_t* codes, int64_t rows, int64_t cols, int64
  * mean the same values under that format.  Each 128-wide block dot product is accumulated by the
  * tensor core in fp32 (TMEM); the promotion across K blocks is an fp32 FMA chain in g order.
  * workspace: bfp8_gemm_block128_workspace_bytes(m, n, k) bytes, 256-byte aligned (may be NULL if 0).
+ *   Its first 64 KB hold arrival counters: they must be zero before the first call and every call
+ *   leaves them zero, so one zero-initialised buffer serves any sequence of calls on one stream.
+ *   Calls that may overlap on the device need separate workspaces.
  * status |= WAIT_TIMEOUT if an internal barrier wait gave up (output is then undefined). */
 size_t bfp8_gemm_block128_workspace_bytes(int64_t m, int64_t n, int64_t k);
 int bfp8_gemm_block128(const uint8_t* a_codes, int64_t lda, const float* a_scales, int64_t ldsa,

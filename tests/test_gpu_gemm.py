@@ -2,8 +2,9 @@
 
 Gate (relative tolerance 1e-2): max |y_kernel - y_oracle| / rms(y_oracle) <= 1e-2 on the values
 before bf16 rounding (fp32 kernel output against the oracle's FP64 sum).  The bf16 output must equal
-the round-to-nearest-even of the kernel's own fp32 output, differ from the oracle's bf16 by at most
-one bf16 ulp per element, and pass the reference's device gate: per-row relative L2 <= 0.01.
+the round-to-nearest-even of the kernel's own fp32 output, sit within one bf16 step (plus twice the
+pre-rounding error) of the oracle's bf16, and pass the reference's device gate: per-row relative
+L2 <= 0.01.
 """
 
 import numpy as np
@@ -33,11 +34,18 @@ def _case_tensors(c):
     return x, w, s, b
 
 
-def _ulp_distance_bf16(a, b):
-    def key(t):
-        i = t.view(torch.int16).to(torch.int32)
-        return torch.where(i < 0, -(i & 0x7FFF), i)
-    return (key(a) - key(b)).abs()
+def _bf16_step(t):
+    """Spacing of bf16 values at |t| (8 significand bits)."""
+    a = t.double().abs().clamp_min(2.0 ** -126)
+    return torch.exp2(torch.floor(torch.log2(a)) - 7)
+
+
+def assert_bf16_close(got16, ybf, pre_rounding_err, label=None):
+    """bf16 results may differ from the oracle's by one rounding step where the two pre-rounding
+    values straddle a rounding boundary; never by more than that plus the pre-rounding error."""
+    diff = (got16.double() - ybf.double()).abs()
+    bound = _bf16_step(ybf) + 2.0 * pre_rounding_err
+    assert bool((diff <= bound).all()), (label, float((diff - bound).max()))
 
 
 def check_against_oracle(gk, x, w, s, b, half, label, y64=None, ybf=None):
@@ -52,10 +60,11 @@ def check_against_oracle(gk, x, w, s, b, half, label, y64=None, ybf=None):
     if rms == 0.0:
         assert not bool(got32.any()) and not bool(got16.any())
         return 0.0
-    metric = float((got32.double() - y64).abs().max()) / rms
+    err = float((got32.double() - y64).abs().max())
+    metric = err / rms
     assert metric <= TOL, (label, metric)
     assert torch.equal(got16, got32.to(torch.bfloat16)), label              # same accumulator, RNE
-    assert int(_ulp_distance_bf16(got16, ybf).max()) <= 1, label
+    assert_bf16_close(got16, ybf, err, label)
     num = (got16.double() - ybf.double()).pow(2).sum(1).sqrt()
     den = ybf.double().pow(2).sum(1).sqrt()
     live = den > 0
@@ -115,6 +124,45 @@ def test_gemm_shapes(gk, m, k, n):
     check_against_oracle(gk, x, w, s, b, True, (m, k, n))
 
 
+@pytest.mark.parametrize("m", [1, 8, 32, 64])
+def test_gemm_decode_bucket(gk, m):
+    # the decode configuration: K=4096, N=14336; both schedules must agree with the oracle,
+    # and the weight-streaming schedule must give identical bits whatever the grid size
+    k, n = 4096, 14336
+    x, w, s, b = _random_problem(m, k, n, seed=100 + m, bias=(m == 8))
+    y64, ybf = block_fp8_ref.reference_rows(x, w, s, native_half=True, bias=b)
+    rms = float(y64.pow(2).mean().sqrt())
+    a_codes, a_scales = gk.quantize_act_1x128(x.cuda(), native_half=True)
+    wc, ws = gk.prepare_weight(w, s, native_half=True)
+    bd = None if b is None else b.cuda()
+    outs = {}
+    for schedule, cap in ((2, 0), (2, 148), (2, 97), (2, 7), (1, 0)):
+        out = gk.gemm_block_fp8(a_codes, a_scales, wc, ws, bias=bd, out_dtype=torch.float32,
+                                schedule=schedule, max_ctas=cap)
+        err = float((out.double().cpu() - y64).abs().max())
+        assert err / rms <= TOL, (schedule, cap, err / rms)
+        outs[(schedule, cap)] = out
+    again = gk.gemm_block_fp8(a_codes, a_scales, wc, ws, bias=bd, out_dtype=torch.float32, schedule=2, max_ctas=97)
+    assert torch.equal(again, outs[(2, 97)])                              # run-to-run identical
+    out16 = gk.gemm_block_fp8(a_codes, a_scales, wc, ws, bias=bd)
+    assert torch.equal(out16, outs[(2, 0)].to(torch.bfloat16))
+
+
+@pytest.mark.parametrize("m,k,n", [(3, 384, 130), (17, 1024, 4096), (100, 512, 300), (128, 14336, 512)])
+def test_gemm_small_m_ragged(gk, m, k, n):
+    x, w, s, b = _random_problem(m, k, n, seed=m + n, bias=True)
+    y64, ybf = block_fp8_ref.reference_rows(x, w, s, native_half=True, bias=b)
+    rms = float(y64.pow(2).mean().sqrt())
+    a_codes, a_scales = gk.quantize_act_1x128(x.cuda(), native_half=True)
+    wc, ws = gk.prepare_weight(w, s, native_half=True)
+    for cap in (0, 5):
+        buf = torch.full((m + 2, n + 8), 0.25, dtype=torch.float32, device="cuda")
+        out = gk.gemm_block_fp8(a_codes, a_scales, wc, ws, bias=b.cuda(), out=buf[:m, :n], out_dtype=torch.float32,
+                                schedule=2, max_ctas=cap)
+        assert float((out.double().cpu() - y64).abs().max()) / rms <= TOL
+        assert bool((buf[m:] == 0.25).all()) and bool((buf[:, n:] == 0.25).all())
+
+
 def test_gemm_output_tail_is_untouched(gk):
     # sentinel columns right of N and rows below M must survive (out-of-bounds write check)
     m, k, n = 70, 256, 200
@@ -126,8 +174,12 @@ def test_gemm_output_tail_is_untouched(gk):
         out = buf[:m, :n]
         gk.gemm_block_fp8(a_codes, a_scales, wc, ws, out=out, out_dtype=dtype)
         assert bool((buf[m:, :] == 0.5).all()) and bool((buf[:, n:] == 0.5).all())
-        y64, _ = block_fp8_ref.reference_rows(x, w, s, native_half=True)
-        assert float((out.double().cpu() - y64).abs().max()) / float(y64.pow(2).mean().sqrt()) <= TOL
+        y64, ybf = block_fp8_ref.reference_rows(x, w, s, native_half=True)
+        rms = float(y64.pow(2).mean().sqrt())
+        if dtype == torch.float32:
+            assert float((out.double().cpu() - y64).abs().max()) / rms <= TOL
+        else:
+            assert_bf16_close(out.cpu(), ybf, 1e-4 * rms)
 
 
 def test_gemm_many_tiles_persistent_loop(gk):
@@ -159,8 +211,9 @@ def test_gemm_prefill_shape_row_sample(gk):
     rows = torch.randperm(m, generator=g)[:48].sort().values
     y64, ybf = block_fp8_ref.reference_rows(x[rows], w_ocp.cpu(), s_ocp.cpu(), native_half=True)
     rms = float(y64.pow(2).mean().sqrt())
-    assert float((out32[rows.cuda()].double().cpu() - y64).abs().max()) / rms <= TOL
-    assert int(_ulp_distance_bf16(out16[rows.cuda()].cpu(), ybf).max()) <= 1
+    err = float((out32[rows.cuda()].double().cpu() - y64).abs().max())
+    assert err / rms <= TOL
+    assert_bf16_close(out16[rows.cuda()].cpu(), ybf, err)
     # linearity in the weight scales (size-independent property): doubling every scale doubles the output exactly
     out_2x = gk.gemm_block_fp8(a_codes, a_scales, wc, ws * 2, out_dtype=torch.float32)
     assert torch.equal(out_2x, out32 * 2)
