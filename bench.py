@@ -10,6 +10,7 @@ FFN projections the path is quoted on; A ~ N(0,1) bf16 quantized 1x128, W ~ N(0,
 
     prefill_up    M=8192  K=4096  N=14336   (default on 1 GPU: the configuration the target is quoted on)
     prefill_down  M=8192  K=14336 N=4096
+    prefill_up_quarter  M=2048 K=4096 N=14336  (small case for profiler captures)
     ffn70b        M=16384 K=8192  N=28672   (default on 2+ GPUs: W split on N over the ranks, A replicated;
                                              total work fixed, so scaling is "strong")
 
@@ -39,6 +40,7 @@ WORKLOADS = {
     "prefill_up": (8192, 4096, 14336),
     "prefill_down": (8192, 14336, 4096),
     "ffn70b": (16384, 8192, 28672),
+    "prefill_up_quarter": (2048, 4096, 14336),     # same kernel and K/N, a quarter of the rows: the size used for ncu captures
 }
 METRIC = "block_fp8_gemm_tflops"
 UNIT = "TFLOP/s"
@@ -48,8 +50,8 @@ L2_FLUSH_BYTES = 256 << 20
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
     ap.add_argument("--e2e-steps", type=int, default=None, help="steps of the host-buffer leg (default: min(steps, 5))")
@@ -80,59 +82,68 @@ def profiled_traffic(workload):
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons, sampled while the timed region runs (read-only queries)."""
+    """SM clock and throttle reasons sampled through NVML (what nvidia-smi reads) while the timed region runs.
 
-    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    Read-only queries from a background thread every ~2 ms; nothing on the GPU is changed.
+    """
+
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+               0x80: "hw_power_brake_slowdown", 0x2: "applications_clocks_setting"}
 
     def __init__(self, gpu_index):
         self.gpu_index = gpu_index
-        self.proc = None
-        self.path = None
+        self.samples = []
+        self.reason_bits = 0
+        self.sm_max = None
+        self.power = []
+        self._stop = False
+        self._thread = None
+
+    def _resolve_handle(self, nv):
+        # CUDA_VISIBLE_DEVICES may renumber devices: match the CUDA device by its PCI bus id
+        import torch
+        try:
+            bus = torch.cuda.get_device_properties(self.gpu_index).pci_bus_id
+            dom = torch.cuda.get_device_properties(self.gpu_index).pci_domain_id
+            dev = torch.cuda.get_device_properties(self.gpu_index).pci_device_id
+            return nv.nvmlDeviceGetHandleByPciBusId(("%08x:%02x:%02x.0" % (dom, bus, dev)).encode())
+        except Exception:
+            return nv.nvmlDeviceGetHandleByIndex(self.gpu_index)
 
     def start(self):
         try:
-            fd, self.path = tempfile.mkstemp(prefix="bfp8_clocks_", suffix=".csv")
-            os.close(fd)
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", str(self.gpu_index), "--query-gpu=" + self.FIELDS,
-                 "--format=csv,noheader,nounits", "-lms", "100"],
-                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
-        except OSError:
-            self.proc = None
+            import pynvml as nv
+            nv.nvmlInit()
+            h = self._resolve_handle(nv)
+            self.sm_max = float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
+        except Exception:
+            return
+        import threading
+
+        def loop():
+            while not self._stop:
+                try:
+                    self.samples.append(float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)))
+                    self.reason_bits |= int(nv.nvmlDeviceGetCurrentClocksEventReasons(h))
+                    self.power.append(nv.nvmlDeviceGetPowerUsage(h) / 1000.0)
+                except Exception:
+                    pass
+                time.sleep(0.002)
+
+        self._thread = threading.Thread(target=loop, daemon=True)
+        self._thread.start()
 
     def stop(self):
-        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        if self.proc is None:
-            return out
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm, reasons, smax = [], set(), None
-        try:
-            with open(self.path) as f:
-                for line in f:
-                    parts = [x.strip() for x in line.split(",")]
-                    if len(parts) < 9:
-                        continue
-                    try:
-                        sm.append(float(parts[1]))
-                        smax = float(parts[2])
-                    except ValueError:
-                        continue
-                    for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"),
-                                         parts[5:9]):
-                        if val.lower().startswith("active"):
-                            reasons.add(name)
-            os.unlink(self.path)
-        except OSError:
-            pass
-        if sm:
-            # samples taken under load are the upper half of the clock distribution's time-line; report the median of all
-            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=smax, reasons=sorted(reasons), samples=len(sm))
+        self._stop = True
+        if self._thread is not None:
+            self._thread.join(timeout=2)
+        out = {"sm_mhz": None, "sm_max_mhz": self.sm_max, "reasons": [], "samples": len(self.samples)}
+        if self.samples:
+            out["sm_mhz"] = statistics.median(self.samples)
+            out["sm_min_mhz"] = min(self.samples)
+            out["power_w_max"] = max(self.power) if self.power else None
+            out["reasons"] = sorted(name for bit, name in self.REASONS.items() if self.reason_bits & bit)
+            out["how"] = "NVML, sampled every ~2 ms during the timed region only"
         return out
 
 

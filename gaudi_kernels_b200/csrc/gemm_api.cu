@@ -5,7 +5,7 @@ namespace bfp8 {
 int launch_gemm_large(const uint8_t* a_codes, int64_t lda, const float* a_scales, int64_t ldsa,
                       const uint8_t* w_codes, int64_t ldw, const float* w_scales, const float* bias, void* out,
                       int out_dtype, int64_t ldo, int64_t m, int64_t n, int64_t k, uint32_t* status_dev,
-                      long long wait_limit, int max_ctas, cudaStream_t st);
+                      long long wait_limit, int max_ctas, int debug, void* trace, cudaStream_t st);
 int launch_gemm_smallm(const uint8_t* a_codes, int64_t lda, const float* a_scales, int64_t ldsa,
                        const uint8_t* w_codes, int64_t ldw, const float* w_scales, const float* bias, void* out,
                        int out_dtype, int64_t ldo, int64_t m, int64_t n, int64_t k, void* workspace,
@@ -37,6 +37,8 @@ extern "C" int bfp8_gemm_block128_ex(const uint8_t* a_codes, int64_t lda, const 
                                      int64_t m, int64_t n, int64_t k,
                                      void* workspace, size_t workspace_bytes, uint32_t* status_dev, void* stream,
                                      int schedule, int max_ctas, int64_t wait_limit_cycles) {
+  const int debug = (schedule >> 8) & 0xff;   // undocumented diagnostics
+  schedule &= 0xff;
   if (!a_codes || !a_scales || !w_codes || !w_scales || !out || !status_dev) return BFP8_ERR_NULL;
   if (m <= 0 || n <= 0 || k <= 0 || m > (1 << 30) || n > (1 << 30) || k > (1 << 30)) return BFP8_ERR_SHAPE;
   if (lda < k || ldw < k || ldo < n || ldsa < m) return BFP8_ERR_SHAPE;
@@ -59,7 +61,7 @@ extern "C" int bfp8_gemm_block128_ex(const uint8_t* a_codes, int64_t lda, const 
                               m, n, k, workspace, status_dev, limit, max_ctas, st);
   }
   return launch_gemm_large(a_codes, lda, a_scales, ldsa, w_codes, ldw, w_scales, bias, out, out_dtype, ldo, m, n, k,
-                           status_dev, limit, max_ctas, st);
+                           status_dev, limit, max_ctas, debug, (debug & 4) ? workspace : nullptr, st);
 }
 
 extern "C" int bfp8_gemm_block128(const uint8_t* a_codes, int64_t lda, const float* a_scales, int64_t ldsa,

@@ -27,7 +27,7 @@ namespace {
 constexpr int BM = 128;            // tile rows (A rows, TMEM lanes)
 constexpr int BN = 256;            // tile columns (W rows, TMEM columns per buffer)
 constexpr int BK = 128;            // one scale block of K
-constexpr int kStages = 3;
+constexpr int kStages = 4;
 constexpr int kEpiWarps = 8;
 constexpr int kThreads = (kEpiWarps + 4) * 32;   // warps 10, 11 only complete the third warpgroup
 constexpr int kTmemCols = 512;     // two accumulator buffers of BN columns
@@ -35,7 +35,8 @@ constexpr int kTmemCols = 512;     // two accumulator buffers of BN columns
 constexpr int kABytes = BM * BK;               // 16 KB
 constexpr int kBBytes = BN * BK;               // 32 KB
 constexpr int kStageBytes = kABytes + kBBytes;
-constexpr int kOutStageBytes = kEpiWarps * 32 * 128 * 2;   // per warp: 32 rows x 128 bf16
+constexpr int kOutWarpBytes = 32 * 64 * 2;                  // per warp: one box of 32 rows x 64 bf16
+constexpr int kOutStageBytes = kEpiWarps * kOutWarpBytes;
 
 struct SmemTail {
   uint64_t full[kStages];
@@ -58,6 +59,8 @@ struct GemmParams {
   int tiles_m, tiles_n;
   long long wait_limit;
   uint32_t* status;
+  long long* trace;        // diagnostics: clock64 stamps of CTA 0 (debug & 4)
+  int debug;               // diagnostics: 1 = epilogue skips TMEM loads and FMAs, 2 = producer re-uses resident stages
 };
 
 // Tiles are walked in bands of 8 tile-rows: consecutive tile indices share W tiles inside a band,
@@ -130,9 +133,13 @@ gemm_block128_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           if (!ok) break;
           const uint32_t full = ptx::smem_u32(&tail->full[stage]);
           const uint32_t a_dst = smem_base + stage * kStageBytes;
+          if ((p.debug & 2) && (phase != 0 || t != static_cast<int>(blockIdx.x))) {
+            ptx::mbar_arrive(full);
+          } else {
           ptx::mbar_arrive_expect_tx(full, kStageBytes);
           ptx::tma_load_2d(a_dst, &tmap_a, full, g * BK, tm * BM);
           ptx::tma_load_2d(a_dst + kABytes, &tmap_w, full, g * BK, tn * BN);
+          }
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
       }
@@ -146,9 +153,11 @@ gemm_block128_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         for (int g = 0; g < G; ++g, ++kb) {
           const uint32_t buf = kb & 1u, acc_phase = (kb >> 1) & 1u;
-          ok = ptx::mbar_wait(ptx::smem_u32(&tail->tmem_empty[buf]), acc_phase ^ 1u, abort_flag, p.wait_limit) &&
-               ptx::mbar_wait(ptx::smem_u32(&tail->full[stage]), phase, abort_flag, p.wait_limit);
+          ok = ptx::mbar_wait(ptx::smem_u32(&tail->tmem_empty[buf]), acc_phase ^ 1u, abort_flag, p.wait_limit);
+          const long long t_a = clock64();
+          ok = ok && ptx::mbar_wait(ptx::smem_u32(&tail->full[stage]), phase, abort_flag, p.wait_limit);
           if (!ok) break;
+          const long long t_b = clock64();
           ptx::tc_fence_after_sync();
           const uint32_t a_addr = smem_base + stage * kStageBytes;
           const uint64_t a_desc = ptx::umma_desc_k128(a_addr);
@@ -159,6 +168,9 @@ gemm_block128_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
             ptx::umma_f8(d, a_desc + 2u * k4, b_desc + 2u * k4, idesc, k4 > 0);
           ptx::umma_commit(ptx::smem_u32(&tail->empty[stage]));
           ptx::umma_commit(ptx::smem_u32(&tail->tmem_full[buf]));
+          if ((p.debug & 4) && blockIdx.x == 0 && kb < 128) {
+            p.trace[kb * 8 + 0] = t_a; p.trace[kb * 8 + 1] = t_b; p.trace[kb * 8 + 2] = clock64();
+          }
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
       }
@@ -167,10 +179,13 @@ gemm_block128_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   } else {
     ptx::setmaxnreg_inc<232>();
     // ------------------------------------------------------------------ epilogue / promotion
+    // TMEM loads complete only at a wait that covers all of a thread's outstanding loads, so the
+    // latency of one 32-column load is hidden behind the FMAs of the previous one (two register
+    // batches), and the first load of the next K block is issued before the last FMAs of this one.
     const int wg = warp >> 2;                      // column half of the tile
     const int quad = warp & 3;                     // TMEM lane quarter this warp may read
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
-    uint8_t* my_stage = out_stage + warp * (32 * 128 * 2);
+    uint8_t* my_stage = out_stage + warp * kOutWarpBytes;
     uint32_t kb = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
@@ -180,84 +195,122 @@ gemm_block128_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       const int col0 = tn * BN + wg * 128;
       const bool row_ok = row < p.m;
       const int nb = col0 >> 7;
-      const bool nb_ok = col0 < p.n;
+      const bool live = row_ok && col0 < p.n;
       const float* sa_ptr = p.a_scales + row;
       const float* sw_ptr = p.w_scales + static_cast<int64_t>(nb) * G;
-      float acc[128];
+      float2 acc[64];
 #pragma unroll
-      for (int j = 0; j < 128; ++j) acc[j] = 0.0f;
-      // scale products are fetched two K blocks ahead of their use
-      float s0 = (row_ok && nb_ok) ? __ldg(sa_ptr) * __ldg(sw_ptr) : 0.0f;
-      float s1 = (row_ok && nb_ok && G > 1) ? __ldg(sa_ptr + p.ldsa) * __ldg(sw_ptr + 1) : 0.0f;
-      for (int g = 0; g < G; ++g, ++kb) {
-        float s2 = 0.0f;
-        if (row_ok && nb_ok && g + 2 < G) s2 = __ldg(sa_ptr + static_cast<int64_t>(g + 2) * p.ldsa) * __ldg(sw_ptr + g + 2);
+      for (int j = 0; j < 64; ++j) acc[j] = make_float2(0.0f, 0.0f);
+      // scales are fetched two K blocks ahead of their use; the product is formed only when needed,
+      // so no load is waited for at the top of the loop
+      float sa0 = live ? __ldg(sa_ptr) : 0.0f, sw0 = live ? __ldg(sw_ptr) : 0.0f;
+      float sa1 = (live && G > 1) ? __ldg(sa_ptr + p.ldsa) : 0.0f, sw1 = (live && G > 1) ? __ldg(sw_ptr + 1) : 0.0f;
+      uint32_t ra[32], rb[32];
+      {
         const uint32_t buf = kb & 1u, acc_phase = (kb >> 1) & 1u;
         ok = ptx::mbar_wait(ptx::smem_u32(&tail->tmem_full[buf]), acc_phase, abort_flag, p.wait_limit);
         if (!ok) break;
         ptx::tc_fence_after_sync();
         const uint32_t taddr = tmem_base + lane_addr + buf * BN + wg * 128;
-        uint32_t ra[16], rb[16];
-        ptx::tmem_ld16(taddr, ra);
-        ptx::tmem_wait_ld16(ra);
-#pragma unroll
-        for (int c = 0; c < 8; c += 2) {
-          ptx::tmem_ld16(taddr + (c + 1) * 16, rb);
-#pragma unroll
-          for (int j = 0; j < 16; ++j) acc[c * 16 + j] = fmaf(__uint_as_float(ra[j]), s0, acc[c * 16 + j]);
-          ptx::tmem_wait_ld16(rb);
-          if (c + 2 < 8) ptx::tmem_ld16(taddr + (c + 2) * 16, ra);
-#pragma unroll
-          for (int j = 0; j < 16; ++j) acc[(c + 1) * 16 + j] = fmaf(__uint_as_float(rb[j]), s0, acc[(c + 1) * 16 + j]);
-          if (c + 2 < 8) ptx::tmem_wait_ld16(ra);
+        ptx::tmem_ld32(taddr, ra);
+        ptx::tmem_ld32(taddr + 32, rb);
+      }
+      for (int g = 0; g < G; ++g, ++kb) {
+        float sa2 = 0.0f, sw2 = 0.0f;
+        if (live && g + 2 < G) {
+          sa2 = __ldg(sa_ptr + static_cast<int64_t>(g + 2) * p.ldsa);
+          sw2 = __ldg(sw_ptr + g + 2);
         }
+        const uint32_t buf = kb & 1u;
+        const uint32_t taddr = tmem_base + lane_addr + buf * BN + wg * 128;
+        const float s = sa0 * sw0;
+        const float2 sv = make_float2(s, s);
+        ptx::tmem_wait_ld32(ra);
+        ptx::tmem_regs_ready32(rb);
+        if ((p.debug & 4) && blockIdx.x == 0 && kb < 128 && warp == 0 && lane == 0) p.trace[kb * 8 + 3] = clock64();
+        if (!(p.debug & 1)) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            acc[j] = __ffma2_rn(make_float2(__uint_as_float(ra[2 * j]), __uint_as_float(ra[2 * j + 1])), sv, acc[j]);
+        }
+        ptx::tmem_ld32(taddr + 64, ra);
+        if (!(p.debug & 1)) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            acc[16 + j] = __ffma2_rn(make_float2(__uint_as_float(rb[2 * j]), __uint_as_float(rb[2 * j + 1])), sv, acc[16 + j]);
+        }
+        ptx::tmem_ld32(taddr + 96, rb);
+        ptx::tmem_wait_ld32(ra);
+        ptx::tmem_regs_ready32(rb);
+        // every column of this buffer is in registers: hand it back to the MMA warp
         ptx::tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&tail->tmem_empty[buf]));
-        s0 = s1;
-        s1 = s2;
+        if ((p.debug & 4) && blockIdx.x == 0 && kb < 128 && warp == 0 && lane == 0) p.trace[kb * 8 + 4] = clock64();
+        if (!(p.debug & 1)) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            acc[32 + j] = __ffma2_rn(make_float2(__uint_as_float(ra[2 * j]), __uint_as_float(ra[2 * j + 1])), sv, acc[32 + j]);
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            acc[48 + j] = __ffma2_rn(make_float2(__uint_as_float(rb[2 * j]), __uint_as_float(rb[2 * j + 1])), sv, acc[48 + j]);
+        }
+        if (g + 1 < G) {
+          // first half of the next K block's buffer
+          const uint32_t nkb = kb + 1, nbuf = nkb & 1u, nphase = (nkb >> 1) & 1u;
+          ok = ptx::mbar_wait(ptx::smem_u32(&tail->tmem_full[nbuf]), nphase, abort_flag, p.wait_limit);
+          if (!ok) break;
+          ptx::tc_fence_after_sync();
+          if ((p.debug & 4) && blockIdx.x == 0 && nkb < 128 && warp == 0 && lane == 0) p.trace[nkb * 8 + 5] = clock64();
+          const uint32_t naddr = tmem_base + lane_addr + nbuf * BN + wg * 128;
+          ptx::tmem_ld32(naddr, ra);
+          ptx::tmem_ld32(naddr + 32, rb);
+        }
+        sa0 = sa1; sw0 = sw1;
+        sa1 = sa2; sw1 = sw2;
       }
       if (!ok) break;
       // ---- tile done: bias, rounding, store
       if (p.bias != nullptr) {
 #pragma unroll
-        for (int j = 0; j < 128; ++j)
-          if (col0 + j < p.n) acc[j] += __ldg(p.bias + col0 + j);
+        for (int j = 0; j < 64; ++j) {
+          if (col0 + 2 * j < p.n) acc[j].x += __ldg(p.bias + col0 + 2 * j);
+          if (col0 + 2 * j + 1 < p.n) acc[j].y += __ldg(p.bias + col0 + 2 * j + 1);
+        }
       }
       if (kOutBf16) {
-        // the previous tile's TMA stores must have finished reading this warp's staging buffer
-        if (lane == 0) ptx::tma_store_wait_read_all();
-        __syncwarp();
-        // two boxes of 32 rows x 64 bf16 (128 B per row), 16-byte chunks XOR-swizzled by row & 7
+        // two passes of one box each: 32 rows x 64 bf16 (128 B per row), 16-byte chunks XOR-swizzled by row & 7
 #pragma unroll
         for (int b = 0; b < 2; ++b) {
+          // the previous TMA store must have finished reading this warp's staging buffer
+          if (lane == 0) ptx::tma_store_wait_read_all();
+          __syncwarp();
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
-            const int e = b * 64 + j * 8;
+            const int e = b * 32 + j * 4;                          // float2 index of the chunk's first pair
             uint4 v;
-            v.x = pack_bf16x2(acc[e + 0], acc[e + 1]);
-            v.y = pack_bf16x2(acc[e + 2], acc[e + 3]);
-            v.z = pack_bf16x2(acc[e + 4], acc[e + 5]);
-            v.w = pack_bf16x2(acc[e + 6], acc[e + 7]);
-            *reinterpret_cast<uint4*>(my_stage + b * 4096 + lane * 128 + ((j ^ (lane & 7)) << 4)) = v;
+            v.x = pack_bf16x2(acc[e + 0].x, acc[e + 0].y);
+            v.y = pack_bf16x2(acc[e + 1].x, acc[e + 1].y);
+            v.z = pack_bf16x2(acc[e + 2].x, acc[e + 2].y);
+            v.w = pack_bf16x2(acc[e + 3].x, acc[e + 3].y);
+            *reinterpret_cast<uint4*>(my_stage + lane * 128 + ((j ^ (lane & 7)) << 4)) = v;
           }
-        }
-        ptx::fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          const int y = tm * BM + quad * 32;
-          if (y < p.m) {
-            if (col0 < p.n) ptx::tma_store_2d(&tmap_out, ptx::smem_u32(my_stage), col0, y);
-            if (col0 + 64 < p.n) ptx::tma_store_2d(&tmap_out, ptx::smem_u32(my_stage + 4096), col0 + 64, y);
+          ptx::fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            const int y = tm * BM + quad * 32;
+            if (y < p.m && col0 + b * 64 < p.n) ptx::tma_store_2d(&tmap_out, ptx::smem_u32(my_stage), col0 + b * 64, y);
+            ptx::tma_store_commit();
           }
-          ptx::tma_store_commit();
         }
       } else {
         if (row_ok) {
           float* o = reinterpret_cast<float*>(p.out) + static_cast<int64_t>(row) * p.ldo + col0;
 #pragma unroll
-          for (int j = 0; j < 128; ++j)
-            if (col0 + j < p.n) o[j] = acc[j];
+          for (int j = 0; j < 64; ++j) {
+            if (col0 + 2 * j < p.n) o[2 * j] = acc[j].x;
+            if (col0 + 2 * j + 1 < p.n) o[2 * j + 1] = acc[j].y;
+          }
         }
       }
     }
@@ -314,7 +367,7 @@ int make_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* bas
 int launch_gemm_large(const uint8_t* a_codes, int64_t lda, const float* a_scales, int64_t ldsa,
                       const uint8_t* w_codes, int64_t ldw, const float* w_scales, const float* bias, void* out,
                       int out_dtype, int64_t ldo, int64_t m, int64_t n, int64_t k, uint32_t* status_dev,
-                      long long wait_limit, int max_ctas, cudaStream_t st) {
+                      long long wait_limit, int max_ctas, int debug, void* trace, cudaStream_t st) {
   alignas(64) CUtensorMap tmap_a, tmap_w, tmap_out;
   int rc = make_tensor_map_2d(&tmap_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, a_codes, k, m, lda, BK, BM);
   if (rc != BFP8_OK) return rc;
@@ -342,6 +395,9 @@ int launch_gemm_large(const uint8_t* a_codes, int64_t lda, const float* a_scales
   p.tiles_n = static_cast<int>((n + BN - 1) / BN);
   p.wait_limit = wait_limit;
   p.status = status_dev;
+  p.debug = debug;
+  p.trace = reinterpret_cast<long long*>(trace);
+  if (trace == nullptr) p.debug &= ~4;
   const int tiles = p.tiles_m * p.tiles_n;
   int grid = sm_count();
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
