@@ -280,7 +280,7 @@ def main():
     # ---- optional: all-gather of the column-sharded bf16 output (outside the timed step)
     gather = None
     if world > 1:
-        full = torch.empty((world, m, n_local), dtype=torch.bfloat16, device=device)
+        full = torch.empty((world * m, n_local), dtype=torch.bfloat16, device=device)
         for _ in range(2):
             dist.all_gather_into_tensor(full, out)
         barrier()

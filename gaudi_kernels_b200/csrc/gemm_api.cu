@@ -5,7 +5,11 @@ namespace bfp8 {
 int launch_gemm_large(const uint8_t* a_codes, int64_t lda, const float* a_scales, int64_t ldsa,
                       const uint8_t* w_codes, int64_t ldw, const float* w_scales, const float* bias, void* out,
                       int out_dtype, int64_t ldo, int64_t m, int64_t n, int64_t k, uint32_t* status_dev,
-                      long long wait_limit, int max_ctas, int debug, void* trace, cudaStream_t st);
+                      long long wait_limit, int max_ctas, cudaStream_t st);
+int launch_gemm_pair(const uint8_t* a_codes, int64_t lda, const float* a_scales, int64_t ldsa,
+                     const uint8_t* w_codes, int64_t ldw, const float* w_scales, const float* bias, void* out,
+                     int out_dtype, int64_t ldo, int64_t m, int64_t n, int64_t k, uint32_t* status_dev,
+                     long long wait_limit, int max_ctas, cudaStream_t st);
 int launch_gemm_smallm(const uint8_t* a_codes, int64_t lda, const float* a_scales, int64_t ldsa,
                        const uint8_t* w_codes, int64_t ldw, const float* w_scales, const float* bias, void* out,
                        int out_dtype, int64_t ldo, int64_t m, int64_t n, int64_t k, void* workspace,
@@ -37,8 +41,6 @@ extern "C" int bfp8_gemm_block128_ex(const uint8_t* a_codes, int64_t lda, const 
                                      int64_t m, int64_t n, int64_t k,
                                      void* workspace, size_t workspace_bytes, uint32_t* status_dev, void* stream,
                                      int schedule, int max_ctas, int64_t wait_limit_cycles) {
-  const int debug = (schedule >> 8) & 0xff;   // undocumented diagnostics
-  schedule &= 0xff;
   if (!a_codes || !a_scales || !w_codes || !w_scales || !out || !status_dev) return BFP8_ERR_NULL;
   if (m <= 0 || n <= 0 || k <= 0 || m > (1 << 30) || n > (1 << 30) || k > (1 << 30)) return BFP8_ERR_SHAPE;
   if (lda < k || ldw < k || ldo < n || ldsa < m) return BFP8_ERR_SHAPE;
@@ -48,7 +50,7 @@ extern "C" int bfp8_gemm_block128_ex(const uint8_t* a_codes, int64_t lda, const 
   if (bias && !aligned(bias, 4)) return BFP8_ERR_ALIGN;
   if (out_dtype == BFP8_OUT_BF16 && (!aligned(out, 16) || ldo % 8 != 0)) return BFP8_ERR_ALIGN;
   if (out_dtype == BFP8_OUT_F32 && !aligned(out, 4)) return BFP8_ERR_ALIGN;
-  if (schedule < 0 || schedule > 2 || (schedule == 2 && (m > kSmallMRows || !smallm_supported(n)))) return BFP8_ERR_SHAPE;
+  if (schedule < 0 || schedule > 3 || (schedule == 2 && (m > kSmallMRows || !smallm_supported(n)))) return BFP8_ERR_SHAPE;
   const bool small = schedule == 2 || (schedule == 0 && m <= kSmallMRows && smallm_supported(n));
   const long long limit = wait_limit_cycles > 0 ? wait_limit_cycles : kDefaultWaitLimit;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -60,8 +62,11 @@ extern "C" int bfp8_gemm_block128_ex(const uint8_t* a_codes, int64_t lda, const 
     return launch_gemm_smallm(a_codes, lda, a_scales, ldsa, w_codes, ldw, w_scales, bias, out, out_dtype, ldo,
                               m, n, k, workspace, status_dev, limit, max_ctas, st);
   }
+  if (schedule == 3)
+    return launch_gemm_pair(a_codes, lda, a_scales, ldsa, w_codes, ldw, w_scales, bias, out, out_dtype, ldo, m, n, k,
+                            status_dev, limit, max_ctas, st);
   return launch_gemm_large(a_codes, lda, a_scales, ldsa, w_codes, ldw, w_scales, bias, out, out_dtype, ldo, m, n, k,
-                           status_dev, limit, max_ctas, debug, (debug & 4) ? workspace : nullptr, st);
+                           status_dev, limit, max_ctas, st);
 }
 
 extern "C" int bfp8_gemm_block128(const uint8_t* a_codes, int64_t lda, const float* a_scales, int64_t ldsa,

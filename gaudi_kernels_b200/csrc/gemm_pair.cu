@@ -14,7 +14,8 @@
 //
 // Per CTA (384 threads): warps 0-7 epilogue (warp w reads TMEM lanes 32 (w%4)..; warpgroup w/4 owns
 // columns 64 (w/4).. of each column half), warp 8 TMA producer, warp 9 TMEM owner and - in the pair's
-// first CTA only - MMA issuer for both CTAs; warps 10-11 idle (their registers go to the epilogue).
+// first CTA only - MMA issuer of the left column half for both CTAs, warp 10 MMA issuer of the right half,
+// warp 11 idle (the third warpgroup's registers go to the epilogue).
 // Barriers: the first CTA's `full` barriers collect the TMA bytes of both CTAs; tcgen05.commit is
 // multicast to both CTAs' `empty` and `tmem_full` barriers; the epilogue warps of both CTAs arrive on
 // the first CTA's `tmem_empty` barriers.  Every wait is bounded and raises BFP8_STATUS_WAIT_TIMEOUT.
@@ -110,13 +111,13 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
                ::"r"(bar), "h"(mask) : "memory");
 }
 __device__ __forceinline__ void mbar_arrive_remote(uint32_t bar_cluster) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster) : "memory");
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster) : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
   return ok != 0;
@@ -177,7 +178,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       ptx::mbar_init(ptx::smem_u32(&tail->full[s]), 1);
-      ptx::mbar_init(ptx::smem_u32(&tail->empty[s]), 1);
+      ptx::mbar_init(ptx::smem_u32(&tail->empty[s]), 2);      // one commit per MMA issuer
     }
     for (int b = 0; b < 4; ++b) {
       ptx::mbar_init(ptx::smem_u32(&tail->tmem_full[b]), 1);
@@ -227,34 +228,31 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           }
         }
       }
-    } else if (warp == kEpiWarps + 1) {
-      // ------------------------------------------------------------------ MMA issuer (first CTA only)
+    } else if (warp == kEpiWarps + 1 || warp == kEpiWarps + 2) {
+      // ------------------------------------------------------------------ MMA issuers (first CTA only)
+      // One issuing thread per column half: their barrier polls and commits overlap, and the tensor
+      // pipe always has work queued from the other half while one of them waits.
       if (lane == 0 && rank == 0) {
+        const int half = warp - (kEpiWarps + 1);
         constexpr uint32_t idesc = ptx::umma_idesc_e4m3(256, 128);
         uint32_t stage = 0, phase = 0, kb = 0;
         bool ok = true;
         for (int t = pair; t < num_tiles && ok; t += num_pairs) {
-          for (int g = 0; g < G && ok; ++g, ++kb) {
-            ok = ptx::mbar_wait(ptx::smem_u32(&tail->full[stage]), phase, abort_flag, p.wait_limit);
+          for (int g = 0; g < G; ++g, ++kb) {
+            const uint32_t buf = (kb & 1u) * 2 + half, acc_phase = (kb >> 1) & 1u;
+            ok = mbar_wait_cluster(ptx::smem_u32(&tail->tmem_empty[buf]), acc_phase ^ 1u, abort_flag, p.wait_limit) &&
+                 ptx::mbar_wait(ptx::smem_u32(&tail->full[stage]), phase, abort_flag, p.wait_limit);
             if (!ok) break;
+            ptx::tc_fence_after_sync();
             const uint32_t base = smem_base + stage * kStageBytes;
             const uint64_t a_desc = ptx::umma_desc_k128(base);
-            const uint32_t acc_phase = (kb >> 1) & 1u;
+            const uint64_t b_desc = ptx::umma_desc_k128(base + kABytes + half * kWHalfBytes);
+            const uint32_t d = tmem_base + buf * 128;
 #pragma unroll
-            for (int half = 0; half < 2; ++half) {
-              const uint32_t buf = (kb & 1u) * 2 + half;
-              ok = mbar_wait_cluster(ptx::smem_u32(&tail->tmem_empty[buf]), acc_phase ^ 1u, abort_flag, p.wait_limit);
-              if (!ok) break;
-              ptx::tc_fence_after_sync();
-              const uint64_t b_desc = ptx::umma_desc_k128(base + kABytes + half * kWHalfBytes);
-              const uint32_t d = tmem_base + buf * 128;
-#pragma unroll
-              for (int k4 = 0; k4 < BK / 32; ++k4)
-                umma_f8_pair(d, a_desc + 2u * k4, b_desc + 2u * k4, idesc, k4 > 0);
-              umma_commit_pair(ptx::smem_u32(&tail->tmem_full[buf]));
-            }
-            if (!ok) break;
-            umma_commit_pair(ptx::smem_u32(&tail->empty[stage]));
+            for (int k4 = 0; k4 < BK / 32; ++k4)
+              umma_f8_pair(d, a_desc + 2u * k4, b_desc + 2u * k4, idesc, k4 > 0);
+            umma_commit_pair(ptx::smem_u32(&tail->tmem_full[buf]));
+            umma_commit_pair(ptx::smem_u32(&tail->empty[stage]));     // second of two arrivals frees the stage
             if (++stage == kStages) { stage = 0; phase ^= 1u; }
           }
         }

@@ -59,8 +59,6 @@ struct GemmParams {
   int tiles_m, tiles_n;
   long long wait_limit;
   uint32_t* status;
-  long long* trace;        // diagnostics: clock64 stamps of CTA 0 (debug & 4)
-  int debug;               // diagnostics: 1 = epilogue skips TMEM loads and FMAs, 2 = producer re-uses resident stages
 };
 
 // Tiles are walked in bands of 8 tile-rows: consecutive tile indices share W tiles inside a band,
@@ -133,13 +131,9 @@ gemm_block128_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           if (!ok) break;
           const uint32_t full = ptx::smem_u32(&tail->full[stage]);
           const uint32_t a_dst = smem_base + stage * kStageBytes;
-          if ((p.debug & 2) && (phase != 0 || t != static_cast<int>(blockIdx.x))) {
-            ptx::mbar_arrive(full);
-          } else {
           ptx::mbar_arrive_expect_tx(full, kStageBytes);
           ptx::tma_load_2d(a_dst, &tmap_a, full, g * BK, tm * BM);
           ptx::tma_load_2d(a_dst + kABytes, &tmap_w, full, g * BK, tn * BN);
-          }
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
       }
@@ -153,11 +147,9 @@ gemm_block128_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         for (int g = 0; g < G; ++g, ++kb) {
           const uint32_t buf = kb & 1u, acc_phase = (kb >> 1) & 1u;
-          ok = ptx::mbar_wait(ptx::smem_u32(&tail->tmem_empty[buf]), acc_phase ^ 1u, abort_flag, p.wait_limit);
-          const long long t_a = clock64();
-          ok = ok && ptx::mbar_wait(ptx::smem_u32(&tail->full[stage]), phase, abort_flag, p.wait_limit);
+          ok = ptx::mbar_wait(ptx::smem_u32(&tail->tmem_empty[buf]), acc_phase ^ 1u, abort_flag, p.wait_limit) &&
+               ptx::mbar_wait(ptx::smem_u32(&tail->full[stage]), phase, abort_flag, p.wait_limit);
           if (!ok) break;
-          const long long t_b = clock64();
           ptx::tc_fence_after_sync();
           const uint32_t a_addr = smem_base + stage * kStageBytes;
           const uint64_t a_desc = ptx::umma_desc_k128(a_addr);
@@ -168,9 +160,6 @@ gemm_block128_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
             ptx::umma_f8(d, a_desc + 2u * k4, b_desc + 2u * k4, idesc, k4 > 0);
           ptx::umma_commit(ptx::smem_u32(&tail->empty[stage]));
           ptx::umma_commit(ptx::smem_u32(&tail->tmem_full[buf]));
-          if ((p.debug & 4) && blockIdx.x == 0 && kb < 128) {
-            p.trace[kb * 8 + 0] = t_a; p.trace[kb * 8 + 1] = t_b; p.trace[kb * 8 + 2] = clock64();
-          }
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
       }
@@ -227,14 +216,13 @@ gemm_block128_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         const float2 sv = make_float2(s, s);
         ptx::tmem_wait_ld32(ra);
         ptx::tmem_regs_ready32(rb);
-        if ((p.debug & 4) && blockIdx.x == 0 && kb < 128 && warp == 0 && lane == 0) p.trace[kb * 8 + 3] = clock64();
-        if (!(p.debug & 1)) {
+        {
 #pragma unroll
           for (int j = 0; j < 16; ++j)
             acc[j] = __ffma2_rn(make_float2(__uint_as_float(ra[2 * j]), __uint_as_float(ra[2 * j + 1])), sv, acc[j]);
         }
         ptx::tmem_ld32(taddr + 64, ra);
-        if (!(p.debug & 1)) {
+        {
 #pragma unroll
           for (int j = 0; j < 16; ++j)
             acc[16 + j] = __ffma2_rn(make_float2(__uint_as_float(rb[2 * j]), __uint_as_float(rb[2 * j + 1])), sv, acc[16 + j]);
@@ -246,8 +234,7 @@ gemm_block128_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         ptx::tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&tail->tmem_empty[buf]));
-        if ((p.debug & 4) && blockIdx.x == 0 && kb < 128 && warp == 0 && lane == 0) p.trace[kb * 8 + 4] = clock64();
-        if (!(p.debug & 1)) {
+        {
 #pragma unroll
           for (int j = 0; j < 16; ++j)
             acc[32 + j] = __ffma2_rn(make_float2(__uint_as_float(ra[2 * j]), __uint_as_float(ra[2 * j + 1])), sv, acc[32 + j]);
@@ -261,8 +248,7 @@ gemm_block128_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           ok = ptx::mbar_wait(ptx::smem_u32(&tail->tmem_full[nbuf]), nphase, abort_flag, p.wait_limit);
           if (!ok) break;
           ptx::tc_fence_after_sync();
-          if ((p.debug & 4) && blockIdx.x == 0 && nkb < 128 && warp == 0 && lane == 0) p.trace[nkb * 8 + 5] = clock64();
-          const uint32_t naddr = tmem_base + lane_addr + nbuf * BN + wg * 128;
+            const uint32_t naddr = tmem_base + lane_addr + nbuf * BN + wg * 128;
           ptx::tmem_ld32(naddr, ra);
           ptx::tmem_ld32(naddr + 32, rb);
         }
@@ -367,7 +353,7 @@ int make_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* bas
 int launch_gemm_large(const uint8_t* a_codes, int64_t lda, const float* a_scales, int64_t ldsa,
                       const uint8_t* w_codes, int64_t ldw, const float* w_scales, const float* bias, void* out,
                       int out_dtype, int64_t ldo, int64_t m, int64_t n, int64_t k, uint32_t* status_dev,
-                      long long wait_limit, int max_ctas, int debug, void* trace, cudaStream_t st) {
+                      long long wait_limit, int max_ctas, cudaStream_t st) {
   alignas(64) CUtensorMap tmap_a, tmap_w, tmap_out;
   int rc = make_tensor_map_2d(&tmap_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, a_codes, k, m, lda, BK, BM);
   if (rc != BFP8_OK) return rc;
@@ -395,9 +381,6 @@ int launch_gemm_large(const uint8_t* a_codes, int64_t lda, const float* a_scales
   p.tiles_n = static_cast<int>((n + BN - 1) / BN);
   p.wait_limit = wait_limit;
   p.status = status_dev;
-  p.debug = debug;
-  p.trace = reinterpret_cast<long long*>(trace);
-  if (trace == nullptr) p.debug &= ~4;
   const int tiles = p.tiles_m * p.tiles_n;
   int grid = sm_count();
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;

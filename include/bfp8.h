@@ -119,7 +119,8 @@ int bfp8_gemm_block128(const uint8_t* a_codes, int64_t lda, const float* a_scale
 
 
 /* Same as bfp8_gemm_block128 with tuning / diagnostic knobs (0 = default for each):
- *   schedule           0 automatic; 1 force the large-tile schedule; 2 force the small-M schedule
+ *   schedule           0 automatic; 1 large-tile schedule (one CTA per 128x256 tile); 2 small-M weight-streaming
+ *                      schedule (m <= 128); 3 CTA-pair schedule (clusters of two CTAs per 256x256 tile)
  *   max_ctas           upper bound on the persistent grid
  *   wait_limit_cycles  SM-clock budget of every internal barrier wait before WAIT_TIMEOUT is raised
  * The reference has no counterpart; its launch geometry is fixed per GUID in

@@ -195,6 +195,26 @@ def test_gemm_many_tiles_persistent_loop(gk):
         assert float((out.double().cpu() - y64).abs().max()) / rms <= TOL, cap
 
 
+@pytest.mark.parametrize("m,k,n", [(256, 256, 256), (300, 384, 520), (1024, 1024, 2048), (130, 208, 257)])
+def test_gemm_pair_schedule_matches_single_cta_schedule(gk, m, k, n):
+    # the CTA-pair schedule (cluster of 2, tcgen05 cta_group::2) must reproduce the single-CTA schedule bit for bit
+    x, w, s, b = _random_problem(m, k, n, seed=m + k + n, bias=True)
+    a_codes, a_scales = gk.quantize_act_1x128(x.cuda(), native_half=True)
+    wc, ws = gk.prepare_weight(w, s, native_half=True)
+    y64, _ = block_fp8_ref.reference_rows(x, w, s, native_half=True, bias=b)
+    rms = float(y64.pow(2).mean().sqrt())
+    for dtype in (torch.float32, torch.bfloat16):
+        one = gk.gemm_block_fp8(a_codes, a_scales, wc, ws, bias=b.cuda(), out_dtype=dtype, schedule=1)
+        for cap in (0, 4, 2):
+            buf = torch.full((m + 1, (n + 7) // 8 * 8 + 8), 3.0, dtype=dtype, device="cuda")
+            two = gk.gemm_block_fp8(a_codes, a_scales, wc, ws, bias=b.cuda(), out=buf[:m, :n], out_dtype=dtype,
+                                    schedule=3, max_ctas=cap)
+            assert torch.equal(one, two), (dtype, cap)
+            assert bool((buf[m:] == 3.0).all()) and bool((buf[:, n:] == 3.0).all())
+        if dtype == torch.float32:
+            assert float((one.double().cpu() - y64).abs().max()) / rms <= TOL
+
+
 def test_gemm_prefill_shape_row_sample(gk):
     # the prefill configuration M=8192, K=4096, N=14336 at full size, checked on a seeded sample of rows
     m, k, n = 8192, 4096, 14336
