@@ -112,4 +112,14 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   return r;
 }
 
+// 64 output columns of one row as bf16 with plain stores, only the first `valid` of them.  Used for the
+// last box of a row when N is not a multiple of 8: a bulk tensor store writes whole 16-byte chunks.
+__device__ __forceinline__ void store_row_bf16_guarded(uint16_t* o, const float2* a, int valid) {
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    if (2 * j < valid) o[2 * j] = static_cast<uint16_t>(float_to_bf16_bits(a[j].x));
+    if (2 * j + 1 < valid) o[2 * j + 1] = static_cast<uint16_t>(float_to_bf16_bits(a[j].y));
+  }
+}
+
 }  // namespace bfp8

@@ -356,7 +356,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             if (col0 + 2 * j + 1 < p.n) a[j].y += __ldg(p.bias + col0 + 2 * j + 1);
           }
         }
-        if (kOutBf16) {
+        if (kOutBf16 && (p.n & 7) != 0 && col0 + 64 > p.n) {
+          // ragged right edge that is not 16-byte granular: guarded element stores
+          if (row_ok && col0 < p.n)
+            store_row_bf16_guarded(reinterpret_cast<uint16_t*>(p.out) + static_cast<int64_t>(row) * p.ldo + col0, a,
+                                   p.n - col0);
+        } else if (kOutBf16) {
           // one box: 32 rows x 64 bf16 (128 B per row), 16-byte chunks XOR-swizzled by row & 7
           if (lane == 0) ptx::tma_store_wait_read_all();
           __syncwarp();

@@ -268,6 +268,13 @@ gemm_block128_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         // two passes of one box each: 32 rows x 64 bf16 (128 B per row), 16-byte chunks XOR-swizzled by row & 7
 #pragma unroll
         for (int b = 0; b < 2; ++b) {
+          if ((p.n & 7) != 0 && col0 + b * 64 + 64 > p.n) {
+            // ragged right edge that is not 16-byte granular: guarded element stores
+            if (row_ok && col0 + b * 64 < p.n)
+              store_row_bf16_guarded(reinterpret_cast<uint16_t*>(p.out) + static_cast<int64_t>(row) * p.ldo + col0 + b * 64,
+                                     acc + b * 32, p.n - (col0 + b * 64));
+            continue;
+          }
           // the previous TMA store must have finished reading this warp's staging buffer
           if (lane == 0) ptx::tma_store_wait_read_all();
           __syncwarp();

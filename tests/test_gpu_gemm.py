@@ -165,12 +165,12 @@ def test_gemm_small_m_ragged(gk, m, k, n):
 
 def test_gemm_output_tail_is_untouched(gk):
     # sentinel columns right of N and rows below M must survive (out-of-bounds write check)
-    m, k, n = 70, 256, 200
+    m, k, n = 70, 256, 203
     x, w, s, _ = _random_problem(m, k, n, seed=5)
     a_codes, a_scales = gk.quantize_act_1x128(x.cuda(), native_half=True)
     wc, ws = gk.prepare_weight(w, s, native_half=True)
     for dtype in (torch.bfloat16, torch.float32):
-        buf = torch.full((m + 3, n + 24), 0.5, dtype=dtype, device="cuda")
+        buf = torch.full((m + 3, n + 29), 0.5, dtype=dtype, device="cuda")       # row pitch 232: a multiple of 8
         out = buf[:m, :n]
         gk.gemm_block_fp8(a_codes, a_scales, wc, ws, out=out, out_dtype=dtype)
         assert bool((buf[m:, :] == 0.5).all()) and bool((buf[:, n:] == 0.5).all())
