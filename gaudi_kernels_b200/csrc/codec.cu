@@ -310,6 +310,7 @@ extern "C" const char* bfp8_error_string(int code) {
     case BFP8_ERR_WORKSPACE: return "workspace too small";
     case BFP8_ERR_CUDA: return "CUDA call failed";
     case BFP8_ERR_UNSUPPORTED: return "device is not sm_100";
+    case BFP8_ERR_TOO_LARGE: return "problem exceeds the fixed scratch of the no-allocation entry point";
     default: return "unknown error";
   }
 }

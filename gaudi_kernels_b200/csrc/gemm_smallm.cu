@@ -389,4 +389,75 @@ int launch_gemm_smallm(const uint8_t* a_codes, int64_t lda, const float* a_scale
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Entry point that allocates nothing
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+// Scratch of bfp8_gemm_block128_noalloc: the 64 KB of per-tile arrival counters followed by room for two
+// fp32 partial tiles (32 padded rows x 128 columns) from each of up to 160 CTAs - 5,308,416 bytes in all.
+// It is part of the library image: every GPU that loads libbfp8.so holds it until the process exits.
+constexpr int kNoAllocMaxRows = 32;
+constexpr int kNoAllocMaxCtas = 160;
+constexpr size_t kNoAllocScratchBytes =
+    kCounterBytes + static_cast<size_t>(kNoAllocMaxCtas) * 2 * kNoAllocMaxRows * BN * sizeof(float);
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+
+// Device address of the scratch array on the current device.  In host code the array's name is only a
+// handle for the runtime, never a pointer a kernel may use, so the address is asked for once per device
+// (with that device current) and remembered.
+int noalloc_scratch_address(void** out) {
+  static void* address[64] = {};
+  int dev = 0;
+  BFP8_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return BFP8_ERR_UNSUPPORTED;
+  if (address[dev] == nullptr) {
+    void* p = nullptr;
+    BFP8_CUDA_TRY(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+    if (p == nullptr) return BFP8_ERR_CUDA;
+    address[dev] = p;
+  }
+  *out = address[dev];
+  return BFP8_OK;
+}
+
+}  // namespace
 }  // namespace bfp8
+
+// The small-M GEMM for callers that cannot hand the library a workspace because they cannot allocate
+// one at the point of the call - an inference server that gave all device memory to its own pools at
+// start-up and runs its decode steps with the allocator closed, or host code running where CUDA
+// allocation calls are not allowed (they synchronise the whole device).  The scratch the weight-streaming
+// schedule needs lives in a fixed array inside the library instead; the price is a hard size limit.
+//
+// Same arguments and results as bfp8_gemm_block128 (minus the workspace), for m <= 32 and
+// n <= 2,097,152.  Larger problems return BFP8_ERR_TOO_LARGE and launch nothing.  The call performs no
+// cudaMalloc / cudaFree and uses no allocating library routine.  The first call on each device looks up
+// the scratch array's device address and raises the kernel's shared-memory limit; make that first call
+// before any stream capture.  All calls on a device share the one array: the counters are cleared on the
+// stream at the start of every call (the partial sums need no clearing, they are written before they are
+// read), and two calls that may overlap on the GPU - different streams, or different host threads - race
+// on it.
+extern "C" int bfp8_gemm_block128_noalloc(const uint8_t* a_codes, int64_t lda, const float* a_scales, int64_t ldsa,
+                                          const uint8_t* w_codes, int64_t ldw, const float* w_scales,
+                                          const float* bias, void* out, int out_dtype, int64_t ldo,
+                                          int64_t m, int64_t n, int64_t k, uint32_t* status_dev, void* stream) {
+  using namespace bfp8;
+  if (!a_codes || !a_scales || !w_codes || !w_scales || !out || !status_dev) return BFP8_ERR_NULL;
+  if (m <= 0 || n <= 0 || k <= 0 || k > (1 << 30)) return BFP8_ERR_SHAPE;
+  if (m > kNoAllocMaxRows || !smallm_supported(n)) return BFP8_ERR_TOO_LARGE;
+  if (lda < k || ldw < k || ldo < n || ldsa < m) return BFP8_ERR_SHAPE;
+  if (out_dtype != BFP8_OUT_F32 && out_dtype != BFP8_OUT_BF16) return BFP8_ERR_SHAPE;
+  if (!aligned(a_codes, 16) || !aligned(w_codes, 16) || lda % 16 != 0 || ldw % 16 != 0) return BFP8_ERR_ALIGN;
+  if (!aligned(a_scales, 4) || !aligned(w_scales, 4) || !aligned(status_dev, 4)) return BFP8_ERR_ALIGN;
+  if (bias && !aligned(bias, 4)) return BFP8_ERR_ALIGN;
+  if (!aligned(out, out_dtype == BFP8_OUT_BF16 ? 2 : 4)) return BFP8_ERR_ALIGN;
+  void* scratch = nullptr;
+  const int rc = noalloc_scratch_address(&scratch);
+  if (rc != BFP8_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t counter_bytes = static_cast<size_t>((n + BN - 1) / BN) * sizeof(uint32_t);
+  BFP8_CUDA_TRY(cudaMemsetAsync(scratch, 0, counter_bytes, st));
+  return launch_gemm_smallm(a_codes, lda, a_scales, ldsa, w_codes, ldw, w_scales, bias, out, out_dtype, ldo, m, n, k,
+                            scratch, status_dev, /*wait_limit=*/2000000000LL, kNoAllocMaxCtas, st);
+}

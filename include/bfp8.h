@@ -34,6 +34,7 @@ extern "C" {
 #define BFP8_ERR_WORKSPACE   -4   /* workspace smaller than bfp8_*_workspace_bytes() */
 #define BFP8_ERR_CUDA        -5   /* a CUDA runtime / driver call failed (see bfp8_last_cuda_error) */
 #define BFP8_ERR_UNSUPPORTED -6   /* the device is not an sm_100 part */
+#define BFP8_ERR_TOO_LARGE   -7   /* the problem exceeds the fixed scratch of bfp8_gemm_block128_noalloc */
 
 #define BFP8_STATUS_NONFINITE_CODE 0x1u  /* an input byte was 0x7f or 0xff (OCP E4M3FN NaN) */
 #define BFP8_STATUS_BAD_SCALE      0x2u  /* a scale was negative, non-finite, or overflowed when doubled */
@@ -132,6 +133,22 @@ int bfp8_gemm_block128_ex(const uint8_t* a_codes, int64_t lda, const float* a_sc
                           void* workspace, size_t workspace_bytes,
                           uint32_t* status_dev, void* stream,
                           int schedule, int max_ctas, int64_t wait_limit_cycles);
+
+/* bfp8_gemm_block128 for callers that cannot allocate a workspace where they make the call (for
+ * example a server that handed all device memory to its own pools at start-up, or host code running
+ * where CUDA allocation calls are not allowed).  This entry point has no counterpart in the reference.
+ * The scratch of the small-M schedule lives in a fixed 5,308,416-byte array inside the library (held by
+ * every GPU that loads it), so the size is limited: m <= 32 and n <= 2,097,152, otherwise
+ * BFP8_ERR_TOO_LARGE is returned and nothing is launched.  Arguments and results are those of
+ * bfp8_gemm_block128 without the workspace.  No cudaMalloc / cudaFree or allocating library routine
+ * is called.  The first call on a device performs one-time set-up (it looks up the array's device
+ * address and raises the kernel's shared-memory limit) and should be made before any stream capture.
+ * All calls on a device share the array: calls that may overlap on the GPU race on it. */
+int bfp8_gemm_block128_noalloc(const uint8_t* a_codes, int64_t lda, const float* a_scales, int64_t ldsa,
+                               const uint8_t* w_codes, int64_t ldw, const float* w_scales,
+                               const float* bias, void* out, int out_dtype, int64_t ldo,
+                               int64_t m, int64_t n, int64_t k,
+                               uint32_t* status_dev, void* stream);
 
 #ifdef __cplusplus
 }
