@@ -11,6 +11,7 @@ FFN projections the path is quoted on; A ~ N(0,1) bf16 quantized 1x128, W ~ N(0,
     prefill_up    M=8192  K=4096  N=14336   (default on 1 GPU: the configuration the target is quoted on)
     prefill_down  M=8192  K=14336 N=4096
     prefill_up_quarter  M=2048 K=4096 N=14336  (small case for profiler captures)
+    codec         fp32 [8192, 8192]: the HBM-bound quantize / re-encode / decode kernels, GB/s per kernel
     ffn70b        M=16384 K=8192  N=28672   (default on 2+ GPUs: W split on N over the ranks, A replicated;
                                              total work fixed, so scaling is "strong")
 
@@ -41,6 +42,7 @@ WORKLOADS = {
     "prefill_down": (8192, 14336, 4096),
     "ffn70b": (16384, 8192, 28672),
     "prefill_up_quarter": (2048, 4096, 14336),     # same kernel and K/N, a quarter of the rows: the size used for ncu captures
+    "codec": (8192, 8192, 0),                      # the elementwise codec configuration, fp32 [8192, 8192] (no GEMM)
 }
 METRIC = "block_fp8_gemm_tflops"
 UNIT = "TFLOP/s"
@@ -147,6 +149,70 @@ class ClockSampler:
         return out
 
 
+def bench_codec(torch, lib, device, steps, warmup):
+    """HBM-bound codec kernels on the fp32 [8192, 8192] configuration (N(0, 0.02) with 0.1 % outliers at 50x).
+
+    Inputs rotate over several buffer sets (together far larger than the 126 MB L2), every launch has its own
+    CUDA-event pair, and the figure is algorithmic bytes / median launch time.
+    """
+    r = c = 8192
+    stream = torch.cuda.current_stream().cuda_stream
+    g = torch.Generator(device=device).manual_seed(2)
+    status = torch.zeros(4, dtype=torch.int32, device=device)
+    nb = 4
+    src = []
+    for _ in range(nb):
+        t = torch.randn((r, c), generator=g, device=device) * 0.02
+        mask = torch.rand((r, c), generator=g, device=device) < 1e-3
+        src.append(torch.where(mask, t * 50, t))
+        del t, mask
+    ocp = [torch.empty((r, c), dtype=torch.uint8, device=device) for _ in range(nb)]
+    half = [torch.empty((r, c), dtype=torch.uint8, device=device) for _ in range(nb)]
+    sc = [torch.empty((r // 128, c // 128), dtype=torch.float32, device=device) for _ in range(nb)]
+    sc2 = [torch.empty_like(sc[0]) for _ in range(nb)]
+    xs = [src[i].view(-1)[: r * c // 2].view(r, c // 2).to(torch.bfloat16) for i in range(nb)]   # bf16 [8192, 4096]
+    xs = xs + [x.clone() for x in xs]
+    xc = [torch.empty((r, c // 2), dtype=torch.uint8, device=device) for _ in range(len(xs))]
+    xsc = torch.empty((c // 2 // 128, r), dtype=torch.float32, device=device)
+
+    def timed(fns):
+        n = len(fns)
+        for i in range(max(warmup, 3)):
+            fns[i % n]()
+        torch.cuda.synchronize()
+        ts = []
+        for i in range(max(steps, 8)):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            rc = fns[i % n]()
+            e1.record()
+            torch.cuda.synchronize()
+            assert rc == 0, rc
+            ts.append(e0.elapsed_time(e1))
+        return statistics.median(ts)
+
+    out = {}
+    ms = timed([(lambda i=i: lib.bfp8_quant_block128_f32(src[i].data_ptr(), r, c, c, ocp[i].data_ptr(), c, sc[i].data_ptr(), 0, stream))
+                for i in range(nb)])
+    ms_h = timed([(lambda i=i: lib.bfp8_quant_block128_f32(src[i].data_ptr(), r, c, c, half[i].data_ptr(), c, sc2[i].data_ptr(), 1, stream))
+                  for i in range(nb)])
+    out["quantize_block128_halve"] = {"ms": ms_h, "bytes": r * c * 5, "gbs": r * c * 5 / ms_h / 1e6}
+    out["quantize_block128_ocp"] = {"ms": ms, "bytes": r * c * 5, "gbs": r * c * 5 / ms / 1e6}
+    ms = timed([(lambda i=i: lib.bfp8_reencode_half(ocp[i].data_ptr(), half[(i + 1) % nb].data_ptr(), r * c, sc[i].data_ptr(),
+                                                    sc2[i].data_ptr(), sc[i].numel(), status.data_ptr(), status.data_ptr() + 8, stream))
+                for i in range(nb)])
+    out["reencode_half"] = {"ms": ms, "bytes": r * c * 2, "gbs": r * c * 2 / ms / 1e6}
+    ms = timed([(lambda i=i: lib.bfp8_decode_block128(half[i].data_ptr(), r, c, c, sc2[i].data_ptr(), src[i].data_ptr(), 0, c, stream))
+                for i in range(nb)])
+    out["decode_f32"] = {"ms": ms, "bytes": r * c * 5, "gbs": r * c * 5 / ms / 1e6}
+    m, k = r, c // 2
+    ms = timed([(lambda i=i: lib.bfp8_quant_act_1x128_bf16(xs[i].data_ptr(), m, k, k, xc[i].data_ptr(), k, xsc.data_ptr(), 1, m, 1,
+                                                           None, stream)) for i in range(len(xs))])
+    nbytes = m * k * 3 + (k // 128) * m * 4
+    out["quantize_act_1x128"] = {"ms": ms, "bytes": nbytes, "gbs": nbytes / ms / 1e6, "shape": "bf16 [8192, 4096]"}
+    return out
+
+
 def make_problem(torch, gk, m, k, n_local, n_offset, n_total, device, seed=0):
     """Synthetic operands: bf16 activations and an fp32 weight slice, quantized on the GPU by the library."""
     g = torch.Generator(device="cpu").manual_seed(seed)
@@ -166,6 +232,8 @@ def run_reference(args, workload, m, k, n, world, rank):
     import torch
     from oracle import block_fp8_ref, fp8_codec_ref
     import numpy as np
+    # launchers such as torch.distributed.run pin OMP_NUM_THREADS to 1; the CPU arm uses every host core
+    torch.set_num_threads(max(1, os.cpu_count() or 1))
     rows = max(1, args.cpu_rows)
     rng = np.random.default_rng(0)
     x = torch.from_numpy(rng.standard_normal((rows, k), dtype=np.float32)).to(torch.bfloat16)
@@ -227,7 +295,27 @@ def main():
         dist.init_process_group("nccl", device_id=device)
     import gaudi_kernels_b200 as gk
     from gaudi_kernels_b200 import _lib
-    _lib.load()
+    lib = _lib.load()
+
+    if workload == "codec":
+        # codec kernels only (single GPU; every rank would do identical work)
+        if rank == 0:
+            res = bench_codec(torch, lib, device, args.steps, args.warmup)
+            _, _, hbm_gbs = measured_peaks()
+            main_k = res["quantize_block128_halve"]
+            line = {"metric": "codec_hbm_gbs", "value": main_k["gbs"], "unit": "GB/s", "n_gpus": 1, "steps": max(args.steps, 8),
+                    "warmup": max(args.warmup, 3), "ms_per_step": main_k["ms"], "higher_is_better": True, "scaling": "weak",
+                    "vs_baseline": None, "dtype": "f32 -> e4m3 (u8)", "data": "synthetic",
+                    "config": {"workload": "codec fp32 [8192, 8192]: quantize 128x128 + halve (5 B/elem)",
+                               "l2": "inputs rotate over 4 buffer sets (1 GiB), far larger than L2"},
+                    "roofline": {"bound": "hbm", "achieved": main_k["gbs"], "peak": hbm_gbs, "unit": "GB/s",
+                                 "frac": main_k["gbs"] / hbm_gbs, "peak_source": "MEASURED_PEAKS.json hbm_gbs - of measured",
+                                 "traffic": None, "kernel": "quant_block128_kernel"},
+                    "kernels": res, "gpu_launches": 5 * max(args.steps, 8)}
+            print(json.dumps(line), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     if n % (128 * world) != 0:
         raise SystemExit("N must split into 128-aligned slices")
@@ -350,12 +438,17 @@ def main():
         "gpu_launches": args.steps,
         "wall_s_timed_region": t_wall,
     }
+    if world == 1:
+        codec = bench_codec(torch, lib, device, 8, 3)
+        line["codec_hbm_gbs"] = {k: round(v["gbs"], 1) for k, v in codec.items()}
+        line["codec_hbm_frac_of_measured"] = {k: round(v["gbs"] / hbm_gbs, 3) for k, v in codec.items()}
     if gather is not None:
         line["gather"] = gather
     if e2e is not None:
         line["e2e"] = e2e
     if world == 1 and not args.no_cpu_baseline:
         from oracle import block_fp8_ref
+        torch.set_num_threads(max(1, os.cpu_count() or 1))
         rows = max(1, args.cpu_rows)
         xs = x[:rows].contiguous()
         wc, sc = w_ocp.cpu(), s_ocp.cpu()

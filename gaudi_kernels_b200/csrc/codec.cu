@@ -101,7 +101,7 @@ __global__ void double_scales_kernel(const float* __restrict__ in, float* __rest
 constexpr int kQuantThreads = 256;
 
 template <bool kVec>
-__global__ void __launch_bounds__(kQuantThreads)
+__global__ void __launch_bounds__(kQuantThreads, 3)
 quant_block128_kernel(const float* __restrict__ w, int64_t rows, int64_t cols, int64_t ld,
                       uint8_t* __restrict__ codes, int64_t ld_codes, float* __restrict__ scales,
                       int col_blocks, int native_half) {
@@ -136,14 +136,14 @@ quant_block128_kernel(const float* __restrict__ w, int64_t rows, int64_t cols, i
 #pragma unroll
   for (int i = 1; i < kQuantThreads / 32; ++i) amax = fmaxf(amax, warp_max[i]);
   const float s = scale_from_amax(amax);
+  const float rcp = __frcp_rn(s);
   if (threadIdx.x == 0)
     scales[static_cast<int64_t>(blockIdx.y) * col_blocks + blockIdx.x] = native_half ? __fmul_rn(s, 2.0f) : s;
 #pragma unroll
   for (int i = 0; i < 16; ++i) {
     const int64_t r = r0 + warp + 8 * i;
     if (r >= rows) continue;
-    uint32_t q = cvt_e4m3x4(scaled_clamped(v[i].x, s), scaled_clamped(v[i].y, s),
-                            scaled_clamped(v[i].z, s), scaled_clamped(v[i].w, s));
+    uint32_t q = quant_e4m3x4(v[i].x, v[i].y, v[i].z, v[i].w, s, rcp);
     if (native_half) q = half_e4m3x4(q);
     uint8_t* p = codes + r * ld_codes + c;
     if (kVec) {
@@ -158,76 +158,95 @@ quant_block128_kernel(const float* __restrict__ w, int64_t rows, int64_t cols, i
 
 // ---------------------------------------------------------------------------------------------
 // K3  1x128 activation quantizer: a half-warp (16 lanes x 8 bf16 = 16 B each) owns one group.
+//     A CTA of 16 half-warps walks whole rows (several rows at once when a row has fewer than 16
+//     groups), so no index division sits in the loop; each half-warp has two groups in flight.
 // ---------------------------------------------------------------------------------------------
 constexpr int kActThreads = 256;
+constexpr int kActPer = 2;            // groups per half-warp and iteration
 
-template <bool kVec, typename Idx>
-__global__ void __launch_bounds__(kActThreads)
+template <bool kVec>
+__global__ void __launch_bounds__(kActThreads, 6)
 quant_act_1x128_kernel(const uint16_t* __restrict__ x, int64_t m, int64_t k, int64_t ldx,
                        uint8_t* __restrict__ codes, int64_t ld_codes, float* __restrict__ scales,
-                       int64_t ssm, int64_t ssg, int64_t groups, int native_half,
+                       int64_t ssm, int64_t ssg, int groups, int native_half,
                        uint32_t* __restrict__ status) {
-  const int sub = threadIdx.x & 15;
-  uint32_t nonfinite = 0;                                      // lane inside the half-warp
-  // Idx is 32-bit whenever m * groups fits, which keeps the row/group split cheap.
-  const Idx hw = static_cast<Idx>((static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 4);
-  const Idx nhw = static_cast<Idx>((static_cast<int64_t>(gridDim.x) * blockDim.x) >> 4);
-  const Idx total = static_cast<Idx>(m * groups);
-  const Idx ngroups = static_cast<Idx>(groups);
-  // All 32 lanes of a warp run the same number of iterations (shuffles below are warp-wide).
-  const Idx iters = (total + nhw - 1) / nhw;
-  for (Idx it = 0; it < iters; ++it) {
-    const Idx idx = hw + it * nhw;
-    const bool live = idx < total;
-    const int64_t row = live ? idx / ngroups : 0, g = live ? idx % ngroups : 0;
-    const int64_t col = g * 128 + sub * 8;
-    float f[8];
+  const int sub = threadIdx.x & 15;                            // lane inside the half-warp
+  const int hw = threadIdx.x >> 4;                             // half-warp inside the CTA, 0..15
+  uint32_t nonfinite = 0;
+  int rows_per_cta, row_off, g_first, g_step;
+  if (groups >= 16) {
+    rows_per_cta = 1; row_off = 0; g_first = hw; g_step = 16;
+  } else {
+    rows_per_cta = 16 / groups; row_off = hw / groups; g_first = hw % groups; g_step = 16;   // one group per row
+    if (row_off >= rows_per_cta) g_first = groups;             // spare half-warps stay idle
+  }
+  // warp-uniform trip counts: shuffles below are warp-wide
+  const int g_iters = (groups + 16 * kActPer - 1) / (16 * kActPer);
+  for (int64_t row_base = static_cast<int64_t>(blockIdx.x) * rows_per_cta; row_base < m;
+       row_base += static_cast<int64_t>(gridDim.x) * rows_per_cta) {
+    const int64_t row = row_base + row_off;
+    const bool row_ok = row < m;
+    const uint16_t* xrow = x + row * ldx;
+    uint8_t* crow = codes + row * ld_codes;
+    for (int gi = 0; gi < g_iters; ++gi) {
+      bool live[kActPer];
+      int g[kActPer];
+      int64_t col[kActPer];
+      uint4 raw[kActPer];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) f[j] = 0.0f;
-    if (live) {
-      const uint16_t* p = x + row * ldx + col;
-      if (kVec) {
-        if (col < k) {                                                   // k % 8 == 0 on this path
-          const uint4 raw = __ldcs(reinterpret_cast<const uint4*>(p));
-          const uint32_t* r = reinterpret_cast<const uint32_t*>(&raw);
+      for (int u = 0; u < kActPer; ++u) {
+        g[u] = g_first + (gi * kActPer + u) * g_step;
+        live[u] = row_ok && g[u] < groups;
+        col[u] = static_cast<int64_t>(g[u]) * 128 + sub * 8;
+        raw[u] = make_uint4(0u, 0u, 0u, 0u);
+        if (kVec && live[u] && col[u] < k)                                // k % 8 == 0 on this path
+          raw[u] = __ldcs(reinterpret_cast<const uint4*>(xrow + col[u]));
+      }
+#pragma unroll
+      for (int u = 0; u < kActPer; ++u) {
+        float f[8];
+        if (kVec) {
+          const uint32_t* r = reinterpret_cast<const uint32_t*>(&raw[u]);
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             // a bf16 with all exponent bits set is inf or NaN
             nonfinite |= __vcmpeq2(r[j] & 0x7f807f80u, 0x7f807f80u);
-            f[2 * j] = bf16_bits_to_float(r[j] & 0xffffu);
-            f[2 * j + 1] = bf16_bits_to_float(r[j] >> 16);
+            f[2 * j] = bf16_lo_to_float(r[j]);
+            f[2 * j + 1] = bf16_hi_to_float(r[j]);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            f[j] = 0.0f;
+            if (live[u] && col[u] + j < k) {
+              const uint32_t b = xrow[col[u] + j];
+              nonfinite |= (b & 0x7f80u) == 0x7f80u;
+              f[j] = bf16_bits_to_float(b);
+            }
           }
         }
-      } else {
+        float amax = 0.0f;
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
-          if (col + j < k) {
-            nonfinite |= (p[j] & 0x7f80u) == 0x7f80u;
-            f[j] = bf16_bits_to_float(p[j]);
+        for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(f[j]));
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        const float s = scale_from_amax(amax);
+        const float rcp = __frcp_rn(s);
+        uint32_t q0 = quant_e4m3x4(f[0], f[1], f[2], f[3], s, rcp);
+        uint32_t q1 = quant_e4m3x4(f[4], f[5], f[6], f[7], s, rcp);
+        if (native_half) { q0 = half_e4m3x4(q0); q1 = half_e4m3x4(q1); }
+        if (live[u]) {
+          uint8_t* p = crow + col[u];
+          if (kVec) {
+            if (col[u] < k) __stcs(reinterpret_cast<uint2*>(p), make_uint2(q0, q1));
+          } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              if (col[u] + j < k) p[j] = static_cast<uint8_t>((j < 4 ? q0 : q1) >> (8 * (j & 3)));
           }
+          if (sub == 0) scales[row * ssm + g[u] * ssg] = native_half ? __fmul_rn(s, 2.0f) : s;
+        }
       }
-    }
-    float amax = 0.0f;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(f[j]));
-#pragma unroll
-    for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-    const float s = scale_from_amax(amax);
-    uint32_t q0 = cvt_e4m3x4(scaled_clamped(f[0], s), scaled_clamped(f[1], s),
-                             scaled_clamped(f[2], s), scaled_clamped(f[3], s));
-    uint32_t q1 = cvt_e4m3x4(scaled_clamped(f[4], s), scaled_clamped(f[5], s),
-                             scaled_clamped(f[6], s), scaled_clamped(f[7], s));
-    if (native_half) { q0 = half_e4m3x4(q0); q1 = half_e4m3x4(q1); }
-    if (live) {
-      uint8_t* p = codes + row * ld_codes + col;
-      if (kVec) {
-        if (col < k) __stcs(reinterpret_cast<uint2*>(p), make_uint2(q0, q1));
-      } else {
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-          if (col + j < k) p[j] = static_cast<uint8_t>((j < 4 ? q0 : q1) >> (8 * (j & 3)));
-      }
-      if (sub == 0) scales[row * ssm + g * ssg] = native_half ? __fmul_rn(s, 2.0f) : s;
     }
   }
   if (status != nullptr && __any_sync(0xffffffffu, nonfinite != 0) && (threadIdx.x & 31) == 0)
@@ -364,19 +383,21 @@ extern "C" int bfp8_quant_act_1x128_bf16(const uint16_t* x, int64_t m, int64_t k
     return BFP8_ERR_SHAPE;
   if (!aligned(x, 2) || !aligned(scales, 4)) return BFP8_ERR_ALIGN;
   const int64_t groups = (k + 127) / 128;
+  if (groups > (1 << 24)) return BFP8_ERR_SHAPE;
   const bool vec = aligned(x, 16) && aligned(codes, 8) && ldx % 8 == 0 && ld_codes % 8 == 0 && k % 8 == 0;
-  const int grid = grid_for(m * groups * 16, kActThreads, 8);
+  const int rows_per_cta = groups >= 16 ? 1 : static_cast<int>(16 / groups);
+  const int64_t want = (m + rows_per_cta - 1) / rows_per_cta;
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 6 * 4;         // a few waves of resident CTAs
+  const int grid = static_cast<int>(want < cap ? want : cap);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const bool small = m * groups < (1LL << 30);
-#define BFP8_LAUNCH_ACT(V, I)                                                                        \
-  quant_act_1x128_kernel<V, I><<<grid, kActThreads, 0, st>>>(x, m, k, ldx, codes, ld_codes, scales,  \
-                                                             scale_stride_m, scale_stride_g, groups, native_half, \
-                                                             status_dev)
-  if (vec && small) BFP8_LAUNCH_ACT(true, uint32_t);
-  else if (vec) BFP8_LAUNCH_ACT(true, int64_t);
-  else if (small) BFP8_LAUNCH_ACT(false, uint32_t);
-  else BFP8_LAUNCH_ACT(false, int64_t);
-#undef BFP8_LAUNCH_ACT
+  if (vec)
+    quant_act_1x128_kernel<true><<<grid, kActThreads, 0, st>>>(x, m, k, ldx, codes, ld_codes, scales, scale_stride_m,
+                                                               scale_stride_g, static_cast<int>(groups), native_half,
+                                                               status_dev);
+  else
+    quant_act_1x128_kernel<false><<<grid, kActThreads, 0, st>>>(x, m, k, ldx, codes, ld_codes, scales, scale_stride_m,
+                                                                scale_stride_g, static_cast<int>(groups), native_half,
+                                                                status_dev);
   BFP8_CUDA_TRY(cudaGetLastError());
   return BFP8_OK;
 }

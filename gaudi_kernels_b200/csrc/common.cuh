@@ -97,7 +97,28 @@ __device__ __forceinline__ float scaled_clamped(float x, float scale) {
   return fminf(fmaxf(__fdiv_rn(x, scale), -448.0f), 448.0f);
 }
 
+// Two values -> two OCP E4M3 codes of RNE(clamp(x / scale, +-448)), bit-identical to doing the IEEE
+// division, without a division: with rcp = RN(1 / scale), q = RN(x * rcp) is within one ulp of the
+// quotient, the residual e = x - q * scale is exact in one FMA, and RN(q + e * rcp) is the correctly
+// rounded quotient (Markstein's correction step).  All three steps are packed two-wide fp32 operations.
+// Saturating conversion covers the clamp: anything above 448 rounds or saturates to the code of 448.
+// Quotients too small to be normal fp32 numbers round to a zero code whatever their last bits are.
+__device__ __forceinline__ uint32_t quant_e4m3x2(float x0, float x1, float scale, float rcp) {
+  const float2 x = make_float2(x0, x1), r = make_float2(rcp, rcp);
+  const float2 q = __fmul2_rn(x, r);
+  const float2 e = __ffma2_rn(make_float2(-q.x, -q.y), make_float2(scale, scale), x);
+  const float2 qc = __ffma2_rn(e, r, q);
+  return cvt_e4m3x2(qc.x, qc.y);
+}
+
+__device__ __forceinline__ uint32_t quant_e4m3x4(float a, float b, float c, float d, float scale, float rcp) {
+  return quant_e4m3x2(a, b, scale, rcp) | (quant_e4m3x2(c, d, scale, rcp) << 16);
+}
+
 __device__ __forceinline__ float bf16_bits_to_float(uint32_t b) { return __uint_as_float(b << 16); }
+// The two halves of a packed bf16 pair.
+__device__ __forceinline__ float bf16_lo_to_float(uint32_t pair) { return __uint_as_float(pair << 16); }
+__device__ __forceinline__ float bf16_hi_to_float(uint32_t pair) { return __uint_as_float(pair & 0xffff0000u); }
 
 // fp32 -> bf16 bits, round-to-nearest-even (finite inputs and NaN-preserving).
 __device__ __forceinline__ uint32_t float_to_bf16_bits(float f) {
