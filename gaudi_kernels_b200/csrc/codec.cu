@@ -22,7 +22,7 @@ int sm_count() {
 // K1  re-encode: 1 byte in, 1 byte out per code.
 // ---------------------------------------------------------------------------------------------
 constexpr int kReencodeThreads = 256;
-constexpr int kReencodeUnroll = 4;     // 4 x 16 B in flight per thread
+constexpr int kReencodeUnroll = 8;     // 8 x 16 B in flight per thread
 
 __device__ __forceinline__ void reencode_vec(uint4& v, uint32_t& inexact, uint32_t& bad) {
   uint32_t* w = reinterpret_cast<uint32_t*>(&v);
@@ -202,6 +202,14 @@ quant_act_1x128_kernel(const uint16_t* __restrict__ x, int64_t m, int64_t k, int
         if (kVec && live[u] && col[u] < k)                                // k % 8 == 0 on this path
           raw[u] = __ldcs(reinterpret_cast<const uint4*>(xrow + col[u]));
       }
+      if (kVec && gi == 0) {
+        // warm L2 for this CTA's next row while the current one is reduced and converted
+        const int64_t nrow = row + static_cast<int64_t>(gridDim.x) * rows_per_cta;
+        if (nrow < m && g_first < groups) {
+          const uint16_t* np = x + nrow * ldx + static_cast<int64_t>(g_first) * 128 + sub * 8;
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(np));
+        }
+      }
 #pragma unroll
       for (int u = 0; u < kActPer; ++u) {
         float f[8];
@@ -268,39 +276,55 @@ decode_block128_kernel(const uint8_t* __restrict__ codes, int64_t rows, int64_t 
   const Idx quads_per_row = static_cast<Idx>((cols + 3) >> 2);
   const Idx total = static_cast<Idx>(rows) * quads_per_row;
   const Idx step = static_cast<Idx>(gridDim.x) * blockDim.x;
-  for (Idx i = static_cast<Idx>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += step) {
-    const int64_t r = i / quads_per_row, c = static_cast<int64_t>(i % quads_per_row) << 2;
-    const float s = __ldg(scales + (r >> 7) * col_blocks + (c >> 7));
-    const uint8_t* p = codes + r * ld + c;
-    uint32_t q = 0;
-    if (kVec) {
-      q = __ldcs(reinterpret_cast<const uint32_t*>(p));
-    } else {
+  constexpr int kPer = 4;                                        // independent quads in flight per thread
+  for (Idx base = static_cast<Idx>(blockIdx.x) * blockDim.x + threadIdx.x; base < total; base += step * kPer) {
+    bool live[kPer];
+    int64_t r[kPer], c[kPer];
+    float s[kPer];
+    uint32_t q[kPer];
 #pragma unroll
-      for (int j = 0; j < 4; ++j)
-        if (c + j < cols) q |= static_cast<uint32_t>(p[j]) << (8 * j);
-    }
-    const float2 lo = e4m3x2_to_float2(q & 0xffffu), hi = e4m3x2_to_float2(q >> 16);
-    const float v0 = __fmul_rn(lo.x, s), v1 = __fmul_rn(lo.y, s), v2 = __fmul_rn(hi.x, s), v3 = __fmul_rn(hi.y, s);
-    if (kBf16) {
-      uint16_t* o = reinterpret_cast<uint16_t*>(out) + r * ld_out + c;
+    for (int u = 0; u < kPer; ++u) {
+      const Idx i = base + static_cast<Idx>(u) * step;
+      live[u] = i < total;
+      r[u] = live[u] ? i / quads_per_row : 0;
+      c[u] = live[u] ? static_cast<int64_t>(i % quads_per_row) << 2 : 0;
+      s[u] = __ldg(scales + (r[u] >> 7) * col_blocks + (c[u] >> 7));
+      const uint8_t* p = codes + r[u] * ld + c[u];
+      q[u] = 0;
       if (kVec) {
-        __stcs(reinterpret_cast<uint2*>(o), make_uint2(pack_bf16x2(v0, v1), pack_bf16x2(v2, v3)));
+        if (live[u]) q[u] = __ldcs(reinterpret_cast<const uint32_t*>(p));
       } else {
-        const float v[4] = {v0, v1, v2, v3};
 #pragma unroll
         for (int j = 0; j < 4; ++j)
-          if (c + j < cols) o[j] = static_cast<uint16_t>(float_to_bf16_bits(v[j]));
+          if (live[u] && c[u] + j < cols) q[u] |= static_cast<uint32_t>(p[j]) << (8 * j);
       }
-    } else {
-      float* o = reinterpret_cast<float*>(out) + r * ld_out + c;
-      if (kVec) {
-        __stcs(reinterpret_cast<float4*>(o), make_float4(v0, v1, v2, v3));
-      } else {
-        const float v[4] = {v0, v1, v2, v3};
+    }
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-          if (c + j < cols) o[j] = v[j];
+    for (int u = 0; u < kPer; ++u) {
+      if (!live[u]) continue;
+      const float2 lo = e4m3x2_to_float2(q[u] & 0xffffu), hi = e4m3x2_to_float2(q[u] >> 16);
+      const float v0 = __fmul_rn(lo.x, s[u]), v1 = __fmul_rn(lo.y, s[u]), v2 = __fmul_rn(hi.x, s[u]),
+                  v3 = __fmul_rn(hi.y, s[u]);
+      if (kBf16) {
+        uint16_t* o = reinterpret_cast<uint16_t*>(out) + r[u] * ld_out + c[u];
+        if (kVec) {
+          __stcs(reinterpret_cast<uint2*>(o), make_uint2(pack_bf16x2(v0, v1), pack_bf16x2(v2, v3)));
+        } else {
+          const float v[4] = {v0, v1, v2, v3};
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            if (c[u] + j < cols) o[j] = static_cast<uint16_t>(float_to_bf16_bits(v[j]));
+        }
+      } else {
+        float* o = reinterpret_cast<float*>(out) + r[u] * ld_out + c[u];
+        if (kVec) {
+          __stcs(reinterpret_cast<float4*>(o), make_float4(v0, v1, v2, v3));
+        } else {
+          const float v[4] = {v0, v1, v2, v3};
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            if (c[u] + j < cols) o[j] = v[j];
+        }
       }
     }
   }
