@@ -22,7 +22,7 @@ int sm_count() {
 // K1  re-encode: 1 byte in, 1 byte out per code.
 // ---------------------------------------------------------------------------------------------
 constexpr int kReencodeThreads = 256;
-constexpr int kReencodeUnroll = 8;     // 8 x 16 B in flight per thread
+constexpr int kReencodeUnroll = 4;     // 4 x 16 B in flight per thread
 
 __device__ __forceinline__ void reencode_vec(uint4& v, uint32_t& inexact, uint32_t& bad) {
   uint32_t* w = reinterpret_cast<uint32_t*>(&v);
@@ -36,62 +36,82 @@ __device__ __forceinline__ void reencode_vec(uint4& v, uint32_t& inexact, uint32
 
 __global__ void __launch_bounds__(kReencodeThreads)
 reencode_half_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, int64_t n, int vec_ok,
+                     const float* __restrict__ scales_in, float* __restrict__ scales_out, int64_t n_scales,
                      unsigned long long* __restrict__ rounded, uint32_t* __restrict__ status) {
+  __shared__ uint32_t cta_inexact, cta_bad;
+  if (threadIdx.x == 0) { cta_inexact = 0; cta_bad = 0; }
+  __syncthreads();
   uint32_t inexact = 0, bad = 0;
-  const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  const int64_t nthreads = static_cast<int64_t>(gridDim.x) * blockDim.x;
-  int64_t done = 0;
+  // scales_out = 2 * scales_in with the checks of fp8_codec.py:25-32, spread over the CTAs of this launch
+  {
+    const int64_t per_cta = (n_scales + gridDim.x - 1) / gridDim.x;
+    const int64_t s0 = static_cast<int64_t>(blockIdx.x) * per_cta;
+    const int64_t s1 = s0 + per_cta < n_scales ? s0 + per_cta : n_scales;
+    bool bad_scale = false;
+    for (int64_t i = s0 + threadIdx.x; i < s1; i += kReencodeThreads) {
+      const float sc = scales_in[i];
+      const float d = __fmul_rn(sc, 2.0f);
+      bad_scale |= !(sc >= 0.0f) || isinf(d) || isnan(d);
+      scales_out[i] = d;
+    }
+    if (bad_scale) atomicOr(status, BFP8_STATUS_BAD_SCALE);
+  }
+  // A CTA owns one contiguous chunk of kReencodeUnroll x 256 vectors (16 KB); a warp access is 512 B.
+  const int64_t chunk = static_cast<int64_t>(blockIdx.x) * (kReencodeThreads * kReencodeUnroll);
   if (vec_ok) {
     const int64_t nvec = n >> 4;
     const uint4* vin = reinterpret_cast<const uint4*>(in);
     uint4* vout = reinterpret_cast<uint4*>(out);
-    // Each thread owns kReencodeUnroll vectors per sweep, spaced one grid apart so every warp
-    // access is a contiguous 512 B.
-    for (int64_t base = tid; base < nvec; base += nthreads * kReencodeUnroll) {
-      uint4 v[kReencodeUnroll];
+    uint4 v[kReencodeUnroll];
 #pragma unroll
-      for (int u = 0; u < kReencodeUnroll; ++u) {
-        const int64_t i = base + u * nthreads;
-        if (i < nvec) v[u] = __ldcs(vin + i);
-      }
+    for (int u = 0; u < kReencodeUnroll; ++u) {
+      const int64_t i = chunk + u * kReencodeThreads + threadIdx.x;
+      if (i < nvec) v[u] = __ldcs(vin + i);
+    }
 #pragma unroll
-      for (int u = 0; u < kReencodeUnroll; ++u) {
-        const int64_t i = base + u * nthreads;
-        if (i < nvec) {
-          reencode_vec(v[u], inexact, bad);
-          __stcs(vout + i, v[u]);
-        }
+    for (int u = 0; u < kReencodeUnroll; ++u) {
+      const int64_t i = chunk + u * kReencodeThreads + threadIdx.x;
+      if (i < nvec) {
+        reencode_vec(v[u], inexact, bad);
+        __stcs(vout + i, v[u]);
       }
     }
-    done = nvec << 4;
+    // ragged tail (fewer than 16 bytes): the last CTA's first threads
+    if (blockIdx.x == gridDim.x - 1) {
+      const int64_t i = (nvec << 4) + threadIdx.x;
+      if (i < n) {
+        const uint32_t c = in[i];
+        bad |= nonfinite_x4(c) & 0xffu;
+        inexact += half_inexact_x4(c) & 1u;
+        out[i] = static_cast<uint8_t>(half_e4m3x4(c));
+      }
+    }
+  } else {
+    // unaligned buffers: the same chunk, byte by byte
+    const int64_t first = chunk * 16;
+#pragma unroll 4
+    for (int j = 0; j < kReencodeUnroll * 16; ++j) {
+      const int64_t i = first + static_cast<int64_t>(j) * kReencodeThreads + threadIdx.x;
+      if (i < n) {
+        const uint32_t c = in[i];
+        bad |= nonfinite_x4(c) & 0xffu;
+        inexact += half_inexact_x4(c) & 1u;
+        out[i] = static_cast<uint8_t>(half_e4m3x4(c));
+      }
+    }
   }
-  for (int64_t i = done + tid; i < n; i += nthreads) {           // ragged tail / unaligned buffers
-    const uint32_t c = in[i];
-    bad |= nonfinite_x4(c | 0x00000000u) & 0xffu;
-    inexact += half_inexact_x4(c) & 1u;
-    out[i] = static_cast<uint8_t>(half_e4m3x4(c));
-  }
-  // one atomic per warp at most
+  // warp reduction, then one shared-memory atomic per warp and one global atomic per CTA at most
   inexact = __reduce_add_sync(0xffffffffu, inexact);
   bad = __reduce_or_sync(0xffffffffu, bad);
   if ((threadIdx.x & 31) == 0) {
-    if (inexact) atomicAdd(rounded, static_cast<unsigned long long>(inexact));
-    if (bad) atomicOr(status, BFP8_STATUS_NONFINITE_CODE);
+    if (inexact) atomicAdd(&cta_inexact, inexact);
+    if (bad) atomicOr(&cta_bad, 1u);
   }
-}
-
-// scales_out = 2 * scales_in with the checks of fp8_codec.py:25-32.
-__global__ void double_scales_kernel(const float* __restrict__ in, float* __restrict__ out, int64_t n,
-                                     uint32_t* __restrict__ status) {
-  bool bad = false;
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
-       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const float s = in[i];
-    const float d = __fmul_rn(s, 2.0f);
-    bad |= !(s >= 0.0f) || isinf(d) || isnan(d);
-    out[i] = d;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (cta_inexact) atomicAdd(rounded, static_cast<unsigned long long>(cta_inexact));
+    if (cta_bad) atomicOr(status, BFP8_STATUS_NONFINITE_CODE);
   }
-  if (__any_sync(0xffffffffu, bad) && (threadIdx.x & 31) == 0) atomicOr(status, BFP8_STATUS_BAD_SCALE);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -182,9 +202,8 @@ quant_act_1x128_kernel(const uint16_t* __restrict__ x, int64_t m, int64_t k, int
   }
   // warp-uniform trip counts: shuffles below are warp-wide
   const int g_iters = (groups + 16 * kActPer - 1) / (16 * kActPer);
-  for (int64_t row_base = static_cast<int64_t>(blockIdx.x) * rows_per_cta; row_base < m;
-       row_base += static_cast<int64_t>(gridDim.x) * rows_per_cta) {
-    const int64_t row = row_base + row_off;
+  {
+    const int64_t row = static_cast<int64_t>(blockIdx.x) * rows_per_cta + row_off;
     const bool row_ok = row < m;
     const uint16_t* xrow = x + row * ldx;
     uint8_t* crow = codes + row * ld_codes;
@@ -202,14 +221,6 @@ quant_act_1x128_kernel(const uint16_t* __restrict__ x, int64_t m, int64_t k, int
         if (kVec && live[u] && col[u] < k)                                // k % 8 == 0 on this path
           raw[u] = __ldcs(reinterpret_cast<const uint4*>(xrow + col[u]));
       }
-      if (kVec && gi == 0) {
-        // warm L2 for this CTA's next row while the current one is reduced and converted
-        const int64_t nrow = row + static_cast<int64_t>(gridDim.x) * rows_per_cta;
-        if (nrow < m && g_first < groups) {
-          const uint16_t* np = x + nrow * ldx + static_cast<int64_t>(g_first) * 128 + sub * 8;
-          asm volatile("prefetch.global.L2 [%0];" ::"l"(np));
-        }
-      }
 #pragma unroll
       for (int u = 0; u < kActPer; ++u) {
         float f[8];
@@ -217,8 +228,8 @@ quant_act_1x128_kernel(const uint16_t* __restrict__ x, int64_t m, int64_t k, int
           const uint32_t* r = reinterpret_cast<const uint32_t*>(&raw[u]);
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            // a bf16 with all exponent bits set is inf or NaN
-            nonfinite |= __vcmpeq2(r[j] & 0x7f807f80u, 0x7f807f80u);
+            // a bf16 with all exponent bits set is inf or NaN: only then does adding 0x80 reach bit 15
+            nonfinite |= ((r[j] & 0x7f807f80u) + 0x00800080u) & 0x80008000u;
             f[2 * j] = bf16_lo_to_float(r[j]);
             f[2 * j + 1] = bf16_hi_to_float(r[j]);
           }
@@ -275,65 +286,43 @@ decode_block128_kernel(const uint8_t* __restrict__ codes, int64_t rows, int64_t 
   // Idx is 32-bit whenever rows * ceil(cols/4) fits, which keeps the row/column split cheap.
   const Idx quads_per_row = static_cast<Idx>((cols + 3) >> 2);
   const Idx total = static_cast<Idx>(rows) * quads_per_row;
-  const Idx step = static_cast<Idx>(gridDim.x) * blockDim.x;
-  constexpr int kPer = 4;                                        // independent quads in flight per thread
-  for (Idx base = static_cast<Idx>(blockIdx.x) * blockDim.x + threadIdx.x; base < total; base += step * kPer) {
-    bool live[kPer];
-    int64_t r[kPer], c[kPer];
-    float s[kPer];
-    uint32_t q[kPer];
+  const Idx i = static_cast<Idx>(blockIdx.x) * blockDim.x + threadIdx.x;      // one quad per thread
+  if (i < total) {
+    const int64_t r = i / quads_per_row, c = static_cast<int64_t>(i % quads_per_row) << 2;
+    const float s = __ldg(scales + (r >> 7) * col_blocks + (c >> 7));
+    const uint8_t* p = codes + r * ld + c;
+    uint32_t q = 0;
+    if (kVec) {
+      q = __ldcs(reinterpret_cast<const uint32_t*>(p));
+    } else {
 #pragma unroll
-    for (int u = 0; u < kPer; ++u) {
-      const Idx i = base + static_cast<Idx>(u) * step;
-      live[u] = i < total;
-      r[u] = live[u] ? i / quads_per_row : 0;
-      c[u] = live[u] ? static_cast<int64_t>(i % quads_per_row) << 2 : 0;
-      s[u] = __ldg(scales + (r[u] >> 7) * col_blocks + (c[u] >> 7));
-      const uint8_t* p = codes + r[u] * ld + c[u];
-      q[u] = 0;
+      for (int j = 0; j < 4; ++j)
+        if (c + j < cols) q |= static_cast<uint32_t>(p[j]) << (8 * j);
+    }
+    const float2 lo = e4m3x2_to_float2(q & 0xffffu), hi = e4m3x2_to_float2(q >> 16);
+    const float v0 = __fmul_rn(lo.x, s), v1 = __fmul_rn(lo.y, s), v2 = __fmul_rn(hi.x, s), v3 = __fmul_rn(hi.y, s);
+    if (kBf16) {
+      uint16_t* o = reinterpret_cast<uint16_t*>(out) + r * ld_out + c;
       if (kVec) {
-        if (live[u]) q[u] = __ldcs(reinterpret_cast<const uint32_t*>(p));
+        __stcs(reinterpret_cast<uint2*>(o), make_uint2(pack_bf16x2(v0, v1), pack_bf16x2(v2, v3)));
       } else {
+        const float v[4] = {v0, v1, v2, v3};
 #pragma unroll
         for (int j = 0; j < 4; ++j)
-          if (live[u] && c[u] + j < cols) q[u] |= static_cast<uint32_t>(p[j]) << (8 * j);
+          if (c + j < cols) o[j] = static_cast<uint16_t>(float_to_bf16_bits(v[j]));
       }
-    }
-#pragma unroll
-    for (int u = 0; u < kPer; ++u) {
-      if (!live[u]) continue;
-      const float2 lo = e4m3x2_to_float2(q[u] & 0xffffu), hi = e4m3x2_to_float2(q[u] >> 16);
-      const float v0 = __fmul_rn(lo.x, s[u]), v1 = __fmul_rn(lo.y, s[u]), v2 = __fmul_rn(hi.x, s[u]),
-                  v3 = __fmul_rn(hi.y, s[u]);
-      if (kBf16) {
-        uint16_t* o = reinterpret_cast<uint16_t*>(out) + r[u] * ld_out + c[u];
-        if (kVec) {
-          __stcs(reinterpret_cast<uint2*>(o), make_uint2(pack_bf16x2(v0, v1), pack_bf16x2(v2, v3)));
-        } else {
-          const float v[4] = {v0, v1, v2, v3};
-#pragma unroll
-          for (int j = 0; j < 4; ++j)
-            if (c[u] + j < cols) o[j] = static_cast<uint16_t>(float_to_bf16_bits(v[j]));
-        }
+    } else {
+      float* o = reinterpret_cast<float*>(out) + r * ld_out + c;
+      if (kVec) {
+        __stcs(reinterpret_cast<float4*>(o), make_float4(v0, v1, v2, v3));
       } else {
-        float* o = reinterpret_cast<float*>(out) + r[u] * ld_out + c[u];
-        if (kVec) {
-          __stcs(reinterpret_cast<float4*>(o), make_float4(v0, v1, v2, v3));
-        } else {
-          const float v[4] = {v0, v1, v2, v3};
+        const float v[4] = {v0, v1, v2, v3};
 #pragma unroll
-          for (int j = 0; j < 4; ++j)
-            if (c[u] + j < cols) o[j] = v[j];
-        }
+        for (int j = 0; j < 4; ++j)
+          if (c + j < cols) o[j] = v[j];
       }
     }
   }
-}
-
-int grid_for(int64_t work_items, int threads, int max_ctas_per_sm) {
-  const int64_t want = (work_items + threads - 1) / threads;
-  const int64_t cap = static_cast<int64_t>(sm_count()) * max_ctas_per_sm;
-  return static_cast<int>(want < 1 ? 1 : (want < cap ? want : cap));
 }
 
 }  // namespace bfp8
@@ -367,13 +356,13 @@ extern "C" int bfp8_reencode_half(const uint8_t* codes_in, uint8_t* codes_out, i
   if (!aligned(rounded_dev, 8) || !aligned(status_dev, 4)) return BFP8_ERR_ALIGN;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int vec_ok = aligned(codes_in, 16) && aligned(codes_out, 16);
-  const int grid = grid_for((n + 15) / 16 / kReencodeUnroll + 1, kReencodeThreads, 8);
-  reencode_half_kernel<<<grid, kReencodeThreads, 0, st>>>(codes_in, codes_out, n, vec_ok, rounded_dev, status_dev);
+  const int64_t per_cta = static_cast<int64_t>(kReencodeThreads) * kReencodeUnroll * 16;     // bytes
+  const int64_t ctas = (n + per_cta - 1) / per_cta;
+  if (ctas > 2147483647LL) return BFP8_ERR_SHAPE;
+  const int grid = static_cast<int>(ctas);
+  reencode_half_kernel<<<grid, kReencodeThreads, 0, st>>>(codes_in, codes_out, n, vec_ok, scales_in, scales_out, n_scales,
+                                                          rounded_dev, status_dev);
   BFP8_CUDA_TRY(cudaGetLastError());
-  if (n_scales > 0) {
-    double_scales_kernel<<<grid_for(n_scales, 256, 4), 256, 0, st>>>(scales_in, scales_out, n_scales, status_dev);
-    BFP8_CUDA_TRY(cudaGetLastError());
-  }
   return BFP8_OK;
 }
 
@@ -410,9 +399,9 @@ extern "C" int bfp8_quant_act_1x128_bf16(const uint16_t* x, int64_t m, int64_t k
   if (groups > (1 << 24)) return BFP8_ERR_SHAPE;
   const bool vec = aligned(x, 16) && aligned(codes, 8) && ldx % 8 == 0 && ld_codes % 8 == 0 && k % 8 == 0;
   const int rows_per_cta = groups >= 16 ? 1 : static_cast<int>(16 / groups);
-  const int64_t want = (m + rows_per_cta - 1) / rows_per_cta;
-  const int64_t cap = static_cast<int64_t>(sm_count()) * 6 * 4;         // a few waves of resident CTAs
-  const int grid = static_cast<int>(want < cap ? want : cap);
+  const int64_t want = (m + rows_per_cta - 1) / rows_per_cta;           // one CTA per row (or per 16 / groups rows)
+  if (want > 2147483647LL) return BFP8_ERR_SHAPE;
+  const int grid = static_cast<int>(want);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (vec)
     quant_act_1x128_kernel<true><<<grid, kActThreads, 0, st>>>(x, m, k, ldx, codes, ld_codes, scales, scale_stride_m,
@@ -437,7 +426,9 @@ extern "C" int bfp8_decode_block128(const uint8_t* codes, int64_t rows, int64_t 
   const int cb = static_cast<int>((cols + 127) / 128);
   const bool vec = aligned(codes, 4) && ld % 4 == 0 && cols % 4 == 0 && ld_out % 4 == 0 &&
                    aligned(out, bf16 ? 8 : 16);
-  const int grid = grid_for(rows * ((cols + 3) / 4), kDecodeThreads, 8);
+  const int64_t quads = rows * ((cols + 3) / 4);
+  if ((quads + kDecodeThreads - 1) / kDecodeThreads > 2147483647LL) return BFP8_ERR_SHAPE;
+  const int grid = static_cast<int>((quads + kDecodeThreads - 1) / kDecodeThreads);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const bool small = rows * ((cols + 3) / 4) < (1LL << 30);
 #define BFP8_LAUNCH_DECODE(V, B)                                                                            \

@@ -41,28 +41,39 @@ inline int ensure_smem_limit(Kernel kernel, int bytes, bool (&done)[64]) {
 
 // ---- E4M3 byte arithmetic -----------------------------------------------------------------
 
+// Byte-parallel arithmetic on four packed codes, written with plain 32-bit logic (the __v*4 SIMD
+// intrinsics are multi-instruction emulations on this architecture).
+
+// 0xff in every byte whose magnitude (low 7 bits) is >= 16, i.e. has any of bits 4..6 set.
+__device__ __forceinline__ uint32_t ge16_mask_x4(uint32_t mag) {
+  const uint32_t t = mag & 0x70707070u;
+  const uint32_t one = ((t | (t >> 1) | (t >> 2)) >> 4) & 0x01010101u;     // 0 / 1 per byte
+  return (one << 8) - one;                                                // 0x00 / 0xff per byte, no cross-byte carry
+}
+
 // Half of four packed OCP E4M3FN codes, round-to-nearest-even, in the Gaudi2 encoding
 // (the byte map of python/gaudi_kernels/fp8_codec.py:36-40 evaluated on four bytes at once):
 // magnitude >= 16 loses one exponent step (magnitude - 8); below that the significand shifts right
 // by one and an odd magnitude rounds up only when the shifted value is odd.
 __device__ __forceinline__ uint32_t half_e4m3x4(uint32_t w) {
   const uint32_t mag = w & 0x7f7f7f7fu;
-  const uint32_t ge16 = __vcmpgeu4(mag, 0x10101010u);            // 0xff in bytes with magnitude >= 16
-  const uint32_t hi = __vsub4(mag, 0x08080808u);
-  const uint32_t sh = (mag >> 1) & 0x7f7f7f7fu;
+  const uint32_t ge16 = ge16_mask_x4(mag);
+  // bit 7 is set first so that no byte borrows from its neighbour; bytes below 8 are masked out anyway
+  const uint32_t hi = ((mag | 0x80808080u) - 0x08080808u) & 0x7f7f7f7fu;
+  const uint32_t sh = (mag >> 1) & 0x3f3f3f3fu;
   const uint32_t lo = sh + (mag & sh & 0x01010101u);
-  return (w & 0x80808080u) | (hi & ge16) | (lo & ~ge16);
+  return (w & 0x80808080u) | (lo ^ ((lo ^ hi) & ge16));
 }
 
 // Bit 0 of each byte set where halving that code is inexact (magnitude < 16 and odd).
 __device__ __forceinline__ uint32_t half_inexact_x4(uint32_t w) {
   const uint32_t mag = w & 0x7f7f7f7fu;
-  return mag & 0x01010101u & ~__vcmpgeu4(mag, 0x10101010u);
+  return mag & 0x01010101u & ~ge16_mask_x4(mag);
 }
 
-// Non-zero where a byte is 0x7f or 0xff.
+// Non-zero where a byte is 0x7f or 0xff: only a magnitude of 0x7f carries into bit 7 when 1 is added.
 __device__ __forceinline__ uint32_t nonfinite_x4(uint32_t w) {
-  return __vcmpeq4(w & 0x7f7f7f7fu, 0x7f7f7f7fu);
+  return ((w & 0x7f7f7f7fu) + 0x01010101u) & 0x80808080u;
 }
 
 // Two fp32 -> two OCP E4M3 codes (RNE, finite saturation), `lo` in bits 0-7.
@@ -106,7 +117,7 @@ __device__ __forceinline__ float scaled_clamped(float x, float scale) {
 __device__ __forceinline__ uint32_t quant_e4m3x2(float x0, float x1, float scale, float rcp) {
   const float2 x = make_float2(x0, x1), r = make_float2(rcp, rcp);
   const float2 q = __fmul2_rn(x, r);
-  const float2 e = __ffma2_rn(make_float2(-q.x, -q.y), make_float2(scale, scale), x);
+  const float2 e = __ffma2_rn(q, make_float2(-scale, -scale), x);
   const float2 qc = __ffma2_rn(e, r, q);
   return cvt_e4m3x2(qc.x, qc.y);
 }
