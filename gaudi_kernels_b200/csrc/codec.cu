@@ -30,7 +30,7 @@ __device__ __forceinline__ void reencode_vec(uint4& v, uint32_t& inexact, uint32
   for (int i = 0; i < 4; ++i) {
     bad |= nonfinite_x4(w[i]);
     inexact += __popc(half_inexact_x4(w[i]));
-    w[i] = half_e4m3x4(w[i]);
+    w[i] = half_e4m3x2_cvt(w[i] & 0xffffu) | (half_e4m3x2_cvt(w[i] >> 16) << 16);
   }
 }
 
@@ -163,8 +163,8 @@ quant_block128_kernel(const float* __restrict__ w, int64_t rows, int64_t cols, i
   for (int i = 0; i < 16; ++i) {
     const int64_t r = r0 + warp + 8 * i;
     if (r >= rows) continue;
-    uint32_t q = quant_e4m3x4(v[i].x, v[i].y, v[i].z, v[i].w, s, rcp);
-    if (native_half) q = half_e4m3x4(q);
+    const uint32_t q = native_half ? quant_half_e4m3x4(v[i].x, v[i].y, v[i].z, v[i].w, s, rcp)
+                                   : quant_e4m3x4(v[i].x, v[i].y, v[i].z, v[i].w, s, rcp);
     uint8_t* p = codes + r * ld_codes + c;
     if (kVec) {
       if (c < cols) __stcs(reinterpret_cast<uint32_t*>(p), q);
@@ -228,8 +228,6 @@ quant_act_1x128_kernel(const uint16_t* __restrict__ x, int64_t m, int64_t k, int
           const uint32_t* r = reinterpret_cast<const uint32_t*>(&raw[u]);
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            // a bf16 with all exponent bits set is inf or NaN: only then does adding 0x80 reach bit 15
-            nonfinite |= ((r[j] & 0x7f807f80u) + 0x00800080u) & 0x80008000u;
             f[2 * j] = bf16_lo_to_float(r[j]);
             f[2 * j + 1] = bf16_hi_to_float(r[j]);
           }
@@ -237,23 +235,26 @@ quant_act_1x128_kernel(const uint16_t* __restrict__ x, int64_t m, int64_t k, int
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             f[j] = 0.0f;
-            if (live[u] && col[u] + j < k) {
-              const uint32_t b = xrow[col[u] + j];
-              nonfinite |= (b & 0x7f80u) == 0x7f80u;
-              f[j] = bf16_bits_to_float(b);
-            }
+            if (live[u] && col[u] + j < k) f[j] = bf16_bits_to_float(xrow[col[u] + j]);
           }
         }
+        // NaN-propagating maximum: an inf or NaN anywhere in the group surfaces in amax
         float amax = 0.0f;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(f[j]));
+        for (int j = 0; j < 8; ++j) amax = max_abs_nan(amax, f[j]);
 #pragma unroll
-        for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        for (int o = 8; o > 0; o >>= 1) amax = max_abs_nan(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        nonfinite |= !(amax < __int_as_float(0x7f800000));
         const float s = scale_from_amax(amax);
         const float rcp = __frcp_rn(s);
-        uint32_t q0 = quant_e4m3x4(f[0], f[1], f[2], f[3], s, rcp);
-        uint32_t q1 = quant_e4m3x4(f[4], f[5], f[6], f[7], s, rcp);
-        if (native_half) { q0 = half_e4m3x4(q0); q1 = half_e4m3x4(q1); }
+        uint32_t q0, q1;
+        if (native_half) {
+          q0 = quant_half_e4m3x4(f[0], f[1], f[2], f[3], s, rcp);
+          q1 = quant_half_e4m3x4(f[4], f[5], f[6], f[7], s, rcp);
+        } else {
+          q0 = quant_e4m3x4(f[0], f[1], f[2], f[3], s, rcp);
+          q1 = quant_e4m3x4(f[4], f[5], f[6], f[7], s, rcp);
+        }
         if (live[u]) {
           uint8_t* p = crow + col[u];
           if (kVec) {

@@ -122,6 +122,36 @@ __device__ __forceinline__ uint32_t quant_e4m3x2(float x0, float x1, float scale
   return cvt_e4m3x2(qc.x, qc.y);
 }
 
+// Half of two packed E4M3 codes with round-to-nearest-even, through the conversion units: the codes
+// widen exactly to fp16, halving is exact there, and the narrowing conversion rounds to nearest even
+// (subnormals included) - the same two-step rounding as the byte map of half_e4m3x4 for every finite code.
+__device__ __forceinline__ uint32_t half_e4m3x2_cvt(uint32_t codes) {
+  uint16_t r;
+  asm("{\n\t.reg .b32 t, h;\n\t"
+      "cvt.rn.f16x2.e4m3x2 t, %1;\n\t"
+      "mov.b32 h, 0x38003800;\n\t"                  // 0.5 in both fp16 halves
+      "mul.rn.f16x2 t, t, h;\n\t"
+      "cvt.rn.satfinite.e4m3x2.f16x2 %0, t;\n\t}"
+      : "=h"(r) : "h"(static_cast<uint16_t>(codes)));
+  return r;
+}
+
+// quant_e4m3x2 followed by the half-range step (block_fp8_oracle.py:31-34), both roundings included.
+__device__ __forceinline__ uint32_t quant_half_e4m3x2(float x0, float x1, float scale, float rcp) {
+  return half_e4m3x2_cvt(quant_e4m3x2(x0, x1, scale, rcp));
+}
+
+__device__ __forceinline__ uint32_t quant_half_e4m3x4(float a, float b, float c, float d, float scale, float rcp) {
+  return quant_half_e4m3x2(a, b, scale, rcp) | (quant_half_e4m3x2(c, d, scale, rcp) << 16);
+}
+
+// max(a, |b|) that returns NaN if either is NaN, so one test after a reduction catches any NaN or inf input.
+__device__ __forceinline__ float max_abs_nan(float a, float b) {
+  float r;
+  asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(fabsf(b)));
+  return r;
+}
+
 __device__ __forceinline__ uint32_t quant_e4m3x4(float a, float b, float c, float d, float scale, float rcp) {
   return quant_e4m3x2(a, b, scale, rcp) | (quant_e4m3x2(c, d, scale, rcp) << 16);
 }
