@@ -14,8 +14,10 @@
 // Each K block is accumulated from zero into one of four small TMEM buffers and folded into register
 // accumulators with its scale product sa[g, i] * sw[j/128, g], as in the large-tile schedule.
 //
-// Warp roles (224 threads): warps 0-3 epilogue (thread = weight row), warp 4 TMA producer, warp 5
-// TMEM owner and MMA issuer, warp 6 scale loader: it fetches the scale products of the units ahead
+// Warp roles (256 threads): warps 0-3 epilogue (thread = weight row), warp 4 TMA producer, warp 5
+// TMEM owner and MMA issuer of the even units, warp 7 MMA issuer of the odd units (issuing a unit's four
+// MMAs and its two commits takes one thread longer than the unit's HBM time, so two threads alternate),
+// warp 6 scale loader: it fetches the scale products of the units ahead
 // (global-memory latency is far longer than a unit's 16 KB of HBM time) and parks them in a small
 // shared-memory ring next to the TMEM buffers.  All barrier waits are bounded.
 #include <cuda.h>
@@ -30,7 +32,7 @@ namespace {
 constexpr int BN = 128;            // weight rows per tile = one scale block
 constexpr int BK = 128;
 constexpr int kEpiWarps = 4;
-constexpr int kThreads = (kEpiWarps + 3) * 32;
+constexpr int kThreads = (kEpiWarps + 4) * 32;
 constexpr int kScaleAhead = 4;     // units whose scales are in flight in the loader's registers
 constexpr int kAccBufs = 4;
 constexpr int kWBytes = BN * BK;   // 16 KB of W per unit
@@ -43,6 +45,7 @@ struct Cfg {
   static constexpr int kStageBytes = kWBytes + kABytes;
   static constexpr int kStages = (kSmemBudget / kStageBytes) < kMaxStages ? (kSmemBudget / kStageBytes) : kMaxStages;
   static constexpr int kTmemCols = (kAccBufs * MP) < 32 ? 32 : (kAccBufs * MP);
+  static_assert(kStages % 2 == 0 && kAccBufs % 2 == 0, "the two MMA issuers alternate over stages and TMEM buffers");
 };
 
 struct SmemTail {
@@ -129,8 +132,8 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
+      int tile = static_cast<int>(u0 / G), g = static_cast<int>(u0 % G);       // kept incrementally: no division per unit
       for (long long u = u0; u < u1; ++u) {
-        const int tile = static_cast<int>(u / G), g = static_cast<int>(u % G);
         if (!ptx::mbar_wait(ptx::smem_u32(&tail->empty[stage]), phase ^ 1u, abort_flag, p.wait_limit)) break;
         const uint32_t full = ptx::smem_u32(&tail->full[stage]);
         const uint32_t w_dst = smem_base + stage * C::kStageBytes;
@@ -138,14 +141,16 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         ptx::tma_load_2d(w_dst, &tmap_w, full, g * BK, tile * BN);
         ptx::tma_load_2d(w_dst + kWBytes, &tmap_a, full, g * BK, 0);
         if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+        if (++g == G) { g = 0; ++tile; }
       }
     }
-  } else if (warp == kEpiWarps + 1) {
-    // ------------------------------------------------------------------ MMA issuer
+  } else if (warp == kEpiWarps + 1 || warp == kEpiWarps + 3) {
+    // ------------------------------------------------------------------ MMA issuers (even / odd units)
     if (lane == 0) {
       constexpr uint32_t idesc = ptx::umma_idesc_e4m3(BN, MP);
-      uint32_t stage = 0, phase = 0, kb = 0;
-      for (long long u = u0; u < u1; ++u, ++kb) {
+      const uint32_t first = warp == kEpiWarps + 1 ? 0u : 1u;
+      uint32_t stage = first % C::kStages, phase = 0, kb = first;
+      for (long long u = u0 + first; u < u1; u += 2, kb += 2) {
         const uint32_t buf = kb % kAccBufs, acc_phase = (kb / kAccBufs) & 1u;
         if (!ptx::mbar_wait(ptx::smem_u32(&tail->tmem_empty[buf]), acc_phase ^ 1u, abort_flag, p.wait_limit)) break;
         if (!ptx::mbar_wait(ptx::smem_u32(&tail->full[stage]), phase, abort_flag, p.wait_limit)) break;
@@ -159,15 +164,18 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
           ptx::umma_f8(d, w_desc + 2u * k4, a_desc + 2u * k4, idesc, k4 > 0);
         ptx::umma_commit(ptx::smem_u32(&tail->empty[stage]));
         ptx::umma_commit(ptx::smem_u32(&tail->tmem_full[buf]));
-        if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+        stage += 2;
+        if (stage >= C::kStages) { stage -= C::kStages; phase ^= 1u; }
       }
     }
   } else if (warp == kEpiWarps + 2) {
     // ------------------------------------------------------------------ scale loader
     constexpr int kPer = (MP + 31) / 32;                         // scale products per lane and unit
     float v[kScaleAhead][kPer];
-    auto fetch = [&](long long u, float (&dst)[kPer]) {
-      const int tile = static_cast<int>(u / G), g = static_cast<int>(u % G);
+    int f_tile = static_cast<int>(u0 / G), f_g = static_cast<int>(u0 % G);   // unit the next fetch belongs to
+    auto fetch = [&](long long, float (&dst)[kPer]) {
+      const int tile = f_tile, g = f_g;
+      if (++f_g == G) { f_g = 0; ++f_tile; }
       const float sw = __ldg(p.w_scales + static_cast<int64_t>(tile) * G + g);
       const float* sa = p.a_scales + static_cast<int64_t>(g) * p.ldsa;
 #pragma unroll
@@ -211,8 +219,9 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     uint32_t kb = 0;
     long long seg_start = u0;
     bool ok = true;
+    int tile = static_cast<int>(u0 / G), g = static_cast<int>(u0 % G) - 1;
     for (long long u = u0; u < u1 && ok; ++u, ++kb) {
-      const int tile = static_cast<int>(u / G), g = static_cast<int>(u % G);
+      if (++g == G) { g = 0; ++tile; }
       const uint32_t buf = kb % kAccBufs, acc_phase = (kb / kAccBufs) & 1u;
       ok = ptx::mbar_wait(ptx::smem_u32(&tail->tmem_full[buf]), acc_phase, abort_flag, p.wait_limit) &&
            ptx::mbar_wait(ptx::smem_u32(&tail->scale_full[buf]), acc_phase, abort_flag, p.wait_limit);
@@ -342,12 +351,18 @@ size_t smallm_workspace_bytes(int64_t m, int64_t n, int max_ctas) {
   return kCounterBytes + static_cast<size_t>(max_ctas) * 2 * smallm_padded_rows(m) * BN * sizeof(float);
 }
 
-// Grid size: every CTA should stream the same number of 16 KB units.  When the tile count is close to
-// the SM count, one CTA per whole tile avoids every partial; otherwise the units are split evenly.
+// Grid size: every CTA should stream the same number of 16 KB units, and as few CTAs as possible should
+// end inside a tile (each such end costs a partial-sum round trip through the workspace).  With no more
+// tiles than SMs every tile gets the same whole number of CTAs, so a CTA holds exactly one K range of one
+// tile; with more tiles than SMs the unit list is cut evenly over all SMs.
 int smallm_grid(int64_t tiles, int64_t groups, int sms) {
   const long long units = tiles * groups;
   if (units < sms) return static_cast<int>(units);
-  if (tiles <= sms && tiles * 4 >= static_cast<int64_t>(sms) * 3) return static_cast<int>(tiles);
+  if (tiles <= sms) {
+    long long per_tile = sms / tiles;
+    if (per_tile > groups) per_tile = groups;
+    return static_cast<int>(tiles * per_tile);
+  }
   return sms;
 }
 
