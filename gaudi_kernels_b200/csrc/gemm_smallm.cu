@@ -33,7 +33,7 @@ constexpr int BN = 128;            // weight rows per tile = one scale block
 constexpr int BK = 128;
 constexpr int kEpiWarps = 4;
 constexpr int kThreads = (kEpiWarps + 4) * 32;
-constexpr int kScaleAhead = 4;     // units whose scales are in flight in the loader's registers
+constexpr int kScaleAhead = 8;     // units whose scales are in flight in the loader's registers
 constexpr int kAccBufs = 4;
 constexpr int kWBytes = BN * BK;   // 16 KB of W per unit
 constexpr int kMaxStages = 10;
