@@ -11,6 +11,7 @@ FFN projections the path is quoted on; A ~ N(0,1) bf16 quantized 1x128, W ~ N(0,
     prefill_up    M=8192  K=4096  N=14336   (default on 1 GPU: the configuration the target is quoted on)
     prefill_down  M=8192  K=14336 N=4096
     prefill_up_quarter  M=2048 K=4096 N=14336  (small case for profiler captures)
+    prefill_up_token_channel  M=8192 K=4096 N=14336 with one scale per token and per output channel
     codec         fp32 [8192, 8192]: the HBM-bound quantize / re-encode / decode kernels, GB/s per kernel
     ffn70b        M=16384 K=8192  N=28672   (default on 2+ GPUs: W split on N over the ranks, A replicated;
                                              total work fixed, so scaling is "strong")
@@ -42,6 +43,7 @@ WORKLOADS = {
     "prefill_down": (8192, 14336, 4096),
     "ffn70b": (16384, 8192, 28672),
     "prefill_up_quarter": (2048, 4096, 14336),     # same kernel and K/N, a quarter of the rows: the size used for ncu captures
+    "prefill_up_token_channel": (8192, 4096, 14336),   # same shape, per-token / per-channel scales (no per-block promotion)
     "codec": (8192, 8192, 0),                      # the elementwise codec configuration, fp32 [8192, 8192] (no GEMM)
 }
 METRIC = "block_fp8_gemm_tflops"
@@ -329,14 +331,26 @@ def main():
     n_local = n // world
     n_offset = rank * n_local
     x, w_ocp, s_ocp = make_problem(torch, gk, m, k, n_local, n_offset, n, device)
-    w_codes, w_scales = gk.prepare_weight(w_ocp, s_ocp, native_half=True)
-    a_codes, a_scales = gk.quantize_act_1x128(x.to(device), native_half=True)
+    token_channel = workload.endswith("_token_channel")
+    if token_channel:
+        # per-channel weight scales: the block-quantized codes are kept, one scale per output channel is drawn
+        w_codes = gk.prepare_weight(w_ocp, s_ocp, native_half=True)[0]
+        w_scales = torch.rand(n_local, device=device) * 1e-3 + 1e-4
+        a_codes, a_scales = gk.quantize_act_token(x.to(device), native_half=True)
+        args.no_e2e = True
+        args.no_cpu_baseline = True
+    else:
+        w_codes, w_scales = gk.prepare_weight(w_ocp, s_ocp, native_half=True)
+        a_codes, a_scales = gk.quantize_act_1x128(x.to(device), native_half=True)
     out = torch.empty((m, n_local), dtype=torch.bfloat16, device=device)
     flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=device)
     flops_total = 2.0 * m * k * n                     # whole job, all ranks
 
     def step():
-        gk.gemm_block_fp8(a_codes, a_scales, w_codes, w_scales, out=out, check=False)
+        if token_channel:
+            gk.gemm_token_channel_fp8(a_codes, a_scales, w_codes, w_scales, out=out, check=False)
+        else:
+            gk.gemm_block_fp8(a_codes, a_scales, w_codes, w_scales, out=out, check=False)
 
     def barrier():
         if world > 1:
@@ -439,13 +453,14 @@ def main():
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak_tflops, "unit": "TFLOP/s",
                      "frac": achieved / peak_tflops, "peak_source": peak_how + " - of measured",
                      "frac_of_nominal_4500": achieved / 4500.0,
-                     "traffic": profiled_traffic(workload), "kernel": "gemm_block128_kernel<bf16 out>",
+                     "traffic": profiled_traffic(workload),
+                     "kernel": "gemm_channel_kernel<bf16 out>" if token_channel else "gemm_block128_kernel<bf16 out>",
                      "launch_ms_median": statistics.median(step_ms)},
         "clocks": clocks,
         "gpu_launches": args.steps,
         "wall_s_timed_region": t_wall,
     }
-    if world == 1:
+    if world == 1 and not token_channel:
         codec = bench_codec(torch, lib, device, 8, 3)
         line["codec_hbm_gbs"] = {k: round(v["gbs"], 1) for k, v in codec.items()}
         line["codec_hbm_frac_of_measured"] = {k: round(v["gbs"] / hbm_gbs, 3) for k, v in codec.items()}

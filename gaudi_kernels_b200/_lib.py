@@ -31,6 +31,9 @@ SIGNATURES = {
                                   _i64, _i64, _i64, _ptr, _sz, _ptr, _ptr]),
     "bfp8_gemm_block128_ex": (_int, [_ptr, _i64, _ptr, _i64, _ptr, _i64, _ptr, _ptr, _ptr, _int, _i64,
                                      _i64, _i64, _i64, _ptr, _sz, _ptr, _ptr, _int, _int, _i64]),
+    "bfp8_quant_act_token_bf16": (_int, [_ptr, _i64, _i64, _i64, _ptr, _i64, _ptr, _int, _ptr, _ptr]),
+    "bfp8_gemm_token_channel": (_int, [_ptr, _i64, _ptr, _ptr, _i64, _ptr, _ptr, _ptr, _int, _i64,
+                                       _i64, _i64, _i64, _ptr, _ptr]),
     "bfp8_gemm_block128_noalloc": (_int, [_ptr, _i64, _ptr, _i64, _ptr, _i64, _ptr, _ptr, _ptr, _int, _i64,
                                           _i64, _i64, _i64, _ptr, _ptr]),
 }

@@ -114,6 +114,57 @@ def gemm_block_fp8(a_codes, a_scales, w_codes, w_scales, bias=None, out=None, ou
     return out
 
 
+def gemm_token_channel_fp8(a_codes, a_scales, w_codes, w_scales, bias=None, out=None, out_dtype=torch.bfloat16,
+                           check=True):
+    """out[i, j] = <a_codes[i], w_codes[j]> * a_scales[i] * w_scales[j] (+ bias[j]): per-token / per-channel scales.
+
+    The reference's per-token / per-channel FP8 variant (gk_fp8_token_quant_bf16_v1 -> MME GEMM ->
+    gk_fp8_channel_finish_bf16_v1, csrc/tpc/block_fp8_framework/channel_finish.c:2-18) as one kernel.
+    a_codes E4M3 [M, K], a_scales fp32 [M], w_codes E4M3 [N, K], w_scales fp32 [N], all on one CUDA device.
+    """
+    for name, t in (("a_codes", a_codes), ("w_codes", w_codes)):
+        if (not isinstance(t, torch.Tensor) or t.dtype not in (torch.float8_e4m3fn, torch.uint8) or t.ndim != 2
+                or not t.is_contiguous() or t.device.type != "cuda"):
+            raise ValueError("%s must be a contiguous 2-D E4M3 tensor on a CUDA device" % name)
+    m, k = a_codes.shape
+    n = w_codes.shape[0]
+    if w_codes.shape[1] != k or m < 1 or n < 1 or k < 1:
+        raise ValueError("a_codes [M, K] and w_codes [N, K] must share K")
+    if a_scales.dtype != torch.float32 or a_scales.numel() != m or w_scales.dtype != torch.float32 or w_scales.numel() != n:
+        raise ValueError("a_scales must be FP32 [M] and w_scales FP32 [N]")
+    if out_dtype not in (torch.bfloat16, torch.float32):
+        raise ValueError("out_dtype must be bfloat16 or float32")
+    dev = a_codes.device
+    if bias is not None:
+        if bias.numel() != n:
+            raise ValueError("bias with N elements required")
+        bias = bias.to(device=dev, dtype=torch.float32).contiguous().view(-1)
+    lib = _lib.load()
+    with torch.cuda.device(dev):
+        if k % 16 != 0:
+            kp = (k + 15) // 16 * 16
+            a_codes = torch.nn.functional.pad(a_codes.view(torch.uint8), (0, kp - k))
+            w_codes = torch.nn.functional.pad(w_codes.view(torch.uint8), (0, kp - k))
+        a_scales = a_scales.to(dev).contiguous().view(-1)
+        w_scales = w_scales.to(dev).contiguous().view(-1)
+        if out is None:
+            ldo = n if out_dtype == torch.float32 else (n + 7) // 8 * 8
+            out = torch.empty((m, ldo), dtype=out_dtype, device=dev)[:, :n]
+        else:
+            if out.dtype != out_dtype or tuple(out.shape) != (m, n) or out.stride(1) != 1 or out.device != dev:
+                raise ValueError("out must be [M, N] of out_dtype with unit column stride on the operand device")
+            ldo = out.stride(0)
+        st = _status_buffer(dev)
+        rc = lib.bfp8_gemm_token_channel(
+            a_codes.data_ptr(), a_codes.stride(0), a_scales.data_ptr(), w_codes.data_ptr(), w_codes.stride(0),
+            w_scales.data_ptr(), bias.data_ptr() if bias is not None else None, out.data_ptr(),
+            _lib.OUT_BF16 if out_dtype == torch.bfloat16 else _lib.OUT_F32, ldo, m, n, k, st.data_ptr() + 8, _stream_ptr())
+        _lib.check(rc, "bfp8_gemm_token_channel")
+        if check and _read_status(st)[1] & _lib.STATUS_WAIT_TIMEOUT:
+            raise _lib.Bfp8Error(_WAIT_TIMEOUT_MSG)
+    return out
+
+
 def prepare_weight(weight, scales, native_half=True):
     """Load-time weight preparation: OCP codes + scales -> what gemm_block_fp8 consumes.
 

@@ -274,6 +274,84 @@ quant_act_1x128_kernel(const uint16_t* __restrict__ x, int64_t m, int64_t k, int
 }
 
 // ---------------------------------------------------------------------------------------------
+// K5  per-token activation quantizer: one scale per row (the per-token / per-channel FP8 variant,
+//     csrc/tpc/block_fp8_framework/activation_token.c:4-26).  One CTA per row; the row is read once into
+//     registers (up to 16384 columns; longer rows are read a second time, from L2).
+//     scale = amax / 448 as an IEEE division, with 1 substituted for the amax of an all-zero row (:17).
+// ---------------------------------------------------------------------------------------------
+constexpr int kTokThreads = 256;
+constexpr int kTokVecs = 8;            // 16-byte vectors a thread keeps in registers
+
+__global__ void __launch_bounds__(kTokThreads)
+quant_act_token_kernel(const uint16_t* __restrict__ x, int64_t k, int64_t ldx, uint8_t* __restrict__ codes,
+                       int64_t ld_codes, float* __restrict__ scales, int native_half, int vec_ok,
+                       uint32_t* __restrict__ status) {
+  __shared__ float warp_max[kTokThreads / 32];
+  const int64_t row = blockIdx.x;
+  const uint16_t* xrow = x + row * ldx;
+  uint8_t* crow = codes + row * ld_codes;
+  const int64_t nvec = vec_ok ? (k >> 3) : 0;                    // k % 8 == 0 on the vector path
+  uint4 raw[kTokVecs];
+  float amax = 0.0f;
+#pragma unroll
+  for (int u = 0; u < kTokVecs; ++u) {
+    const int64_t i = static_cast<int64_t>(u) * kTokThreads + threadIdx.x;
+    raw[u] = make_uint4(0u, 0u, 0u, 0u);
+    if (i < nvec) raw[u] = __ldcs(reinterpret_cast<const uint4*>(xrow) + i);
+    const uint32_t* r = reinterpret_cast<const uint32_t*>(&raw[u]);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) amax = max_abs_nan(max_abs_nan(amax, bf16_lo_to_float(r[j])), bf16_hi_to_float(r[j]));
+  }
+  for (int64_t i = static_cast<int64_t>(kTokVecs) * kTokThreads + threadIdx.x; i < nvec; i += kTokThreads) {
+    const uint4 v = *(reinterpret_cast<const uint4*>(xrow) + i);
+    const uint32_t* r = reinterpret_cast<const uint32_t*>(&v);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) amax = max_abs_nan(max_abs_nan(amax, bf16_lo_to_float(r[j])), bf16_hi_to_float(r[j]));
+  }
+  for (int64_t i = (nvec << 3) + threadIdx.x; i < k; i += kTokThreads)       // scalar path / ragged tail
+    amax = max_abs_nan(amax, bf16_bits_to_float(xrow[i]));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = max_abs_nan(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = warp_max[0];
+#pragma unroll
+  for (int i = 1; i < kTokThreads / 32; ++i) amax = max_abs_nan(amax, warp_max[i]);
+  if (!(amax < __int_as_float(0x7f800000)) && threadIdx.x == 0 && status != nullptr)
+    atomicOr(status, BFP8_STATUS_NONFINITE_INPUT);
+  const float s = __fdiv_rn(amax == 0.0f ? 1.0f : amax, 448.0f);
+  const float rcp = __frcp_rn(s);
+  if (threadIdx.x == 0) scales[row] = native_half ? __fmul_rn(s, 2.0f) : s;
+  auto quant8 = [&](const uint4& v) {
+    const uint32_t* r = reinterpret_cast<const uint32_t*>(&v);
+    float f[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { f[2 * j] = bf16_lo_to_float(r[j]); f[2 * j + 1] = bf16_hi_to_float(r[j]); }
+    uint2 q;
+    if (native_half) {
+      q.x = quant_half_e4m3x4(f[0], f[1], f[2], f[3], s, rcp);
+      q.y = quant_half_e4m3x4(f[4], f[5], f[6], f[7], s, rcp);
+    } else {
+      q.x = quant_e4m3x4(f[0], f[1], f[2], f[3], s, rcp);
+      q.y = quant_e4m3x4(f[4], f[5], f[6], f[7], s, rcp);
+    }
+    return q;
+  };
+#pragma unroll
+  for (int u = 0; u < kTokVecs; ++u) {
+    const int64_t i = static_cast<int64_t>(u) * kTokThreads + threadIdx.x;
+    if (i < nvec) __stcs(reinterpret_cast<uint2*>(crow) + i, quant8(raw[u]));
+  }
+  for (int64_t i = static_cast<int64_t>(kTokVecs) * kTokThreads + threadIdx.x; i < nvec; i += kTokThreads)
+    __stcs(reinterpret_cast<uint2*>(crow) + i, quant8(*(reinterpret_cast<const uint4*>(xrow) + i)));
+  for (int64_t i = (nvec << 3) + threadIdx.x; i < k; i += kTokThreads) {
+    const float f = bf16_bits_to_float(xrow[i]);
+    const uint32_t q = native_half ? quant_half_e4m3x2(f, 0.0f, s, rcp) : quant_e4m3x2(f, 0.0f, s, rcp);
+    crow[i] = static_cast<uint8_t>(q);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
 // K4  decode: value(code) * block scale.  A thread turns 4 codes (one 32-bit load) into one
 //     16-byte (fp32) or 8-byte (bf16) store, so both sides of every warp access are contiguous.
 // ---------------------------------------------------------------------------------------------
@@ -444,6 +522,19 @@ extern "C" int bfp8_decode_block128(const uint8_t* codes, int64_t rows, int64_t 
   else if (bf16) BFP8_LAUNCH_DECODE(false, true);
   else BFP8_LAUNCH_DECODE(false, false);
 #undef BFP8_LAUNCH_DECODE
+  BFP8_CUDA_TRY(cudaGetLastError());
+  return BFP8_OK;
+}
+
+extern "C" int bfp8_quant_act_token_bf16(const uint16_t* x, int64_t m, int64_t k, int64_t ldx,
+                                         uint8_t* codes, int64_t ld_codes, float* scales,
+                                         int native_half, uint32_t* status_dev, void* stream) {
+  if (!x || !codes || !scales) return BFP8_ERR_NULL;
+  if (m <= 0 || k <= 0 || ldx < k || ld_codes < k || m > 2147483647LL) return BFP8_ERR_SHAPE;
+  if (!aligned(x, 2) || !aligned(scales, 4)) return BFP8_ERR_ALIGN;
+  const int vec = aligned(x, 16) && aligned(codes, 8) && ldx % 8 == 0 && ld_codes % 8 == 0 && k % 8 == 0;
+  quant_act_token_kernel<<<static_cast<int>(m), kTokThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      x, k, ldx, codes, ld_codes, scales, native_half, vec, status_dev);
   BFP8_CUDA_TRY(cudaGetLastError());
   return BFP8_OK;
 }

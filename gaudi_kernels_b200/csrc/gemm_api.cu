@@ -14,6 +14,10 @@ int launch_gemm_smallm(const uint8_t* a_codes, int64_t lda, const float* a_scale
                        const uint8_t* w_codes, int64_t ldw, const float* w_scales, const float* bias, void* out,
                        int out_dtype, int64_t ldo, int64_t m, int64_t n, int64_t k, void* workspace,
                        uint32_t* status_dev, long long wait_limit, int max_ctas, cudaStream_t st);
+int launch_gemm_channel(const uint8_t* a_codes, int64_t lda, const float* a_scales, const uint8_t* w_codes,
+                        int64_t ldw, const float* w_scales, const float* bias, void* out, int out_dtype, int64_t ldo,
+                        int64_t m, int64_t n, int64_t k, uint32_t* status_dev, long long wait_limit, int max_ctas,
+                        cudaStream_t st);
 size_t smallm_workspace_bytes(int64_t m, int64_t n, int max_ctas);
 bool smallm_supported(int64_t n);
 }
@@ -76,4 +80,21 @@ extern "C" int bfp8_gemm_block128(const uint8_t* a_codes, int64_t lda, const flo
                                   void* workspace, size_t workspace_bytes, uint32_t* status_dev, void* stream) {
   return bfp8_gemm_block128_ex(a_codes, lda, a_scales, ldsa, w_codes, ldw, w_scales, bias, out, out_dtype, ldo,
                                m, n, k, workspace, workspace_bytes, status_dev, stream, 0, 0, 0);
+}
+
+extern "C" int bfp8_gemm_token_channel(const uint8_t* a_codes, int64_t lda, const float* a_scales,
+                                       const uint8_t* w_codes, int64_t ldw, const float* w_scales,
+                                       const float* bias, void* out, int out_dtype, int64_t ldo,
+                                       int64_t m, int64_t n, int64_t k, uint32_t* status_dev, void* stream) {
+  if (!a_codes || !a_scales || !w_codes || !w_scales || !out || !status_dev) return BFP8_ERR_NULL;
+  if (m <= 0 || n <= 0 || k <= 0 || m > (1 << 30) || n > (1 << 30) || k > (1 << 30)) return BFP8_ERR_SHAPE;
+  if (lda < k || ldw < k || ldo < n) return BFP8_ERR_SHAPE;
+  if (out_dtype != BFP8_OUT_F32 && out_dtype != BFP8_OUT_BF16) return BFP8_ERR_SHAPE;
+  if (!aligned(a_codes, 16) || !aligned(w_codes, 16) || lda % 16 != 0 || ldw % 16 != 0) return BFP8_ERR_ALIGN;
+  if (!aligned(a_scales, 4) || !aligned(w_scales, 4) || !aligned(status_dev, 4)) return BFP8_ERR_ALIGN;
+  if (bias && !aligned(bias, 4)) return BFP8_ERR_ALIGN;
+  if (out_dtype == BFP8_OUT_BF16 && (!aligned(out, 16) || ldo % 8 != 0)) return BFP8_ERR_ALIGN;
+  if (out_dtype == BFP8_OUT_F32 && !aligned(out, 4)) return BFP8_ERR_ALIGN;
+  return launch_gemm_channel(a_codes, lda, a_scales, w_codes, ldw, w_scales, bias, out, out_dtype, ldo, m, n, k,
+                             status_dev, kDefaultWaitLimit, 0, static_cast<cudaStream_t>(stream));
 }

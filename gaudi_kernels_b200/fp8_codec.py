@@ -144,6 +144,39 @@ def quantize_act_1x128(x, native_half=False, check_finite=False):
     return codes, scales
 
 
+def quantize_act_token(x, native_half=True, check_finite=False):
+    """bf16 [M, K] -> (E4M3 codes [M, K], fp32 scales [M]): one scale per row.
+
+    The per-token quantizer of the reference's per-token / per-channel FP8 variant
+    (csrc/tpc/block_fp8_framework/activation_token.c:4-26): scale = amax / 448 over the whole row (1 for an
+    all-zero row), code = RNE(x / scale); with native_half (that kernel's only mode) the codes are halved and
+    the stored scale doubled.
+    """
+    if not isinstance(x, torch.Tensor) or x.dtype != torch.bfloat16 or x.ndim != 2 or not x.numel():
+        raise ValueError("expected a nonempty 2-D BF16 tensor")
+    if x.stride(1) != 1:
+        raise ValueError("expected unit stride along the last dimension")
+    lib = _lib.load()
+    dev = _device_for(x)
+    on_host = x.device.type == "cpu"
+    with torch.cuda.device(dev):
+        xd = x.to(dev, non_blocking=True)
+        m, k = xd.shape
+        codes = torch.empty((m, k), dtype=torch.uint8, device=dev)
+        scales = torch.empty((m,), dtype=torch.float32, device=dev)
+        st = _status_buffer(dev) if check_finite else None
+        rc = lib.bfp8_quant_act_token_bf16(xd.data_ptr(), m, k, xd.stride(0), codes.data_ptr(), k, scales.data_ptr(),
+                                           int(bool(native_half)), st.data_ptr() + 8 if check_finite else None,
+                                           _stream_ptr())
+        _lib.check(rc, "bfp8_quant_act_token_bf16")
+        if check_finite and _read_status(st)[1] & _lib.STATUS_NONFINITE_INPUT:
+            raise ValueError("finite original inputs required")
+    codes = codes.view(torch.float8_e4m3fn)
+    if on_host:
+        codes, scales = codes.cpu(), scales.cpu()
+    return codes, scales
+
+
 def decode_e4m3(codes, scales, out_dtype=torch.float32):
     """value(code) * 128x128 block scale -> fp32 or bf16 [R, C].
 

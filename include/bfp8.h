@@ -134,6 +134,28 @@ int bfp8_gemm_block128_ex(const uint8_t* a_codes, int64_t lda, const float* a_sc
                           uint32_t* status_dev, void* stream,
                           int schedule, int max_ctas, int64_t wait_limit_cycles);
 
+/* Per-token activation quantizer, bf16 [m, k] -> E4M3 codes [m, k] + one fp32 scale per row (scales[m]).
+ * Replaces gk_fp8_token_quant_bf16_v1 (csrc/tpc/block_fp8_framework/activation_token.c:4-26): amax over the
+ * whole row, 1 substituted for the amax of an all-zero row (:17), scale = amax / 448 (IEEE division - the
+ * value the kernel's FMA-corrected product computes, activation_quant_common.h:3-7), code = RNE_e4m3(x / scale)
+ * clamped to +-448; native_half != 0 halves the codes (RNE) and stores 2 * scale (:21,24), as that kernel
+ * always does.  status_dev may be NULL; NONFINITE_INPUT is raised for inf / NaN activations. */
+int bfp8_quant_act_token_bf16(const uint16_t* x, int64_t m, int64_t k, int64_t ldx,
+                              uint8_t* codes, int64_t ld_codes, float* scales,
+                              int native_half, uint32_t* status_dev, void* stream);
+
+/* Token/channel-scaled E4M3 GEMM:
+ *   out[i, j] = (sum_t a(i, t) * w(j, t)) * a_scales[i] * w_scales[j] (+ bias[j])
+ * Replaces the Gaudi2 pair "MME GEMM + gk_fp8_channel_finish_bf16_v1"
+ * (csrc/tpc/block_fp8_framework/channel_finish.c:2-18; glue csrc/host/generic_fp8_glue.hpp:56-82): the whole K
+ * range accumulates in TMEM and the finish (partial * act) * w_scale + bias, bf16 rounding included, is the
+ * kernel's epilogue.  Operand and output requirements are those of bfp8_gemm_block128; a_scales is fp32 [m],
+ * w_scales fp32 [n].  No workspace. */
+int bfp8_gemm_token_channel(const uint8_t* a_codes, int64_t lda, const float* a_scales,
+                            const uint8_t* w_codes, int64_t ldw, const float* w_scales,
+                            const float* bias, void* out, int out_dtype, int64_t ldo,
+                            int64_t m, int64_t n, int64_t k, uint32_t* status_dev, void* stream);
+
 /* bfp8_gemm_block128 for callers that cannot allocate a workspace where they make the call (for
  * example a server that handed all device memory to its own pools at start-up, or host code running
  * where CUDA allocation calls are not allowed).  This entry point has no counterpart in the reference.
