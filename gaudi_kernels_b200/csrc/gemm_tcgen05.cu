@@ -57,14 +57,14 @@ struct GemmParams {
   int64_t ldsa, ldo;
   int m, n, k, groups;
   int tiles_m, tiles_n;
+  int band;                // tile-rows per band of the tile walk
   long long wait_limit;
   uint32_t* status;
 };
 
-// Tiles are walked in bands of 8 tile-rows: consecutive tile indices share W tiles inside a band,
+// Tiles are walked in bands of 16 tile-rows: consecutive tile indices share W tiles inside a band,
 // so the CTAs running at any moment touch a compact set of A and W tiles in L2.
-__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& tm, int& tn) {
-  constexpr int kBand = 8;
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int kBand, int& tm, int& tn) {
   const int per_band = kBand * tiles_n;
   const int band = t / per_band;
   const int first = band * kBand;
@@ -125,7 +125,7 @@ gemm_block128_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         int tm, tn;
-        tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+        tile_coords(t, p.tiles_m, p.tiles_n, p.band, tm, tn);
         for (int g = 0; g < G; ++g) {
           ok = ptx::mbar_wait(ptx::smem_u32(&tail->empty[stage]), phase ^ 1u, abort_flag, p.wait_limit);
           if (!ok) break;
@@ -179,7 +179,7 @@ gemm_block128_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     bool ok = true;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
       int tm, tn;
-      tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+      tile_coords(t, p.tiles_m, p.tiles_n, p.band, tm, tn);
       const int row = tm * BM + quad * 32 + lane;
       const int col0 = tn * BN + wg * 128;
       const bool row_ok = row < p.m;
@@ -360,7 +360,7 @@ int make_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* bas
 int launch_gemm_large(const uint8_t* a_codes, int64_t lda, const float* a_scales, int64_t ldsa,
                       const uint8_t* w_codes, int64_t ldw, const float* w_scales, const float* bias, void* out,
                       int out_dtype, int64_t ldo, int64_t m, int64_t n, int64_t k, uint32_t* status_dev,
-                      long long wait_limit, int max_ctas, cudaStream_t st) {
+                      long long wait_limit, int max_ctas, int band, cudaStream_t st) {
   alignas(64) CUtensorMap tmap_a, tmap_w, tmap_out;
   int rc = make_tensor_map_2d(&tmap_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, a_codes, k, m, lda, BK, BM);
   if (rc != BFP8_OK) return rc;
@@ -388,6 +388,7 @@ int launch_gemm_large(const uint8_t* a_codes, int64_t lda, const float* a_scales
   p.tiles_n = static_cast<int>((n + BN - 1) / BN);
   p.wait_limit = wait_limit;
   p.status = status_dev;
+  p.band = band > 0 ? band : 16;
   const int tiles = p.tiles_m * p.tiles_n;
   int grid = sm_count();
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
