@@ -33,6 +33,19 @@ def _workspace(dev, nbytes):
     return ws
 
 
+_HOST_ROW_BLOCK = 1024          # reference() on host tensors pipelines blocks of at least this many rows
+_copy_streams = {}
+
+
+def _copy_stream(dev):
+    """A second stream per device for copying results back while the next block is computed."""
+    st = _copy_streams.get(dev.index)
+    if st is None:
+        st = torch.cuda.Stream(device=dev)
+        _copy_streams[dev.index] = st
+    return st
+
+
 _WAIT_TIMEOUT_MSG = "a bounded wait inside the GEMM kernel expired (BFP8_STATUS_WAIT_TIMEOUT); output is invalid"
 
 
@@ -201,7 +214,6 @@ def reference(x, weight, scales, *, native_half=False, bias=None, out_dtype=torc
     dev = _device_for(x, weight, scales)
     on_host = x.device.type == "cpu"
     with torch.cuda.device(dev):
-        xd = x.to(dev, non_blocking=True).contiguous()
         wd = weight.to(dev, non_blocking=True).contiguous()
         sd = scales.to(dev, non_blocking=True).contiguous()
         st = _status_buffer(dev)
@@ -216,21 +228,47 @@ def reference(x, weight, scales, *, native_half=False, bias=None, out_dtype=torc
         else:
             enc, sw = wd, sd
             finite = ((wd.view(torch.uint8) & 0x7F) != 0x7F).all() & torch.isfinite(sd).all() & (sd >= 0).all()
-        m = xd.shape[0]
-        a_codes = torch.empty((m, k), dtype=torch.uint8, device=dev)
-        a_scales = torch.empty((groups, m), dtype=torch.float32, device=dev)
-        rc = lib.bfp8_quant_act_1x128_bf16(xd.data_ptr(), m, k, xd.stride(0), a_codes.data_ptr(), k,
-                                           a_scales.data_ptr(), 1, m, int(bool(native_half)),
-                                           st.data_ptr() + 8, _stream_ptr())
-        _lib.check(rc, "bfp8_quant_act_1x128_bf16")
-        dev_out = out if (out is not None and out.device.type == "cuda") else None
-        y = gemm_block_fp8(a_codes, a_scales.t(), enc, sw, bias=bias, out=dev_out, out_dtype=out_dtype, check=False)
-        if on_host:
+        m = x.shape[0]
+
+        def run_rows(x_rows, dev_out):
+            """Quantize and multiply one block of activation rows (already on the device)."""
+            mr = x_rows.shape[0]
+            a_codes = torch.empty((mr, k), dtype=torch.uint8, device=dev)
+            a_scales = torch.empty((groups, mr), dtype=torch.float32, device=dev)
+            rc = lib.bfp8_quant_act_1x128_bf16(x_rows.data_ptr(), mr, k, x_rows.stride(0), a_codes.data_ptr(), k,
+                                               a_scales.data_ptr(), 1, mr, int(bool(native_half)),
+                                               st.data_ptr() + 8, _stream_ptr())
+            _lib.check(rc, "bfp8_quant_act_1x128_bf16")
+            return gemm_block_fp8(a_codes, a_scales.t(), enc, sw, bias=bias, out=dev_out, out_dtype=out_dtype,
+                                  check=False)
+
+        if not on_host:
+            dev_out = out if (out is not None and out.device.type == "cuda") else None
+            y = run_rows(x.to(dev).contiguous(), dev_out)
+        else:
             if out is None:
-                out = torch.empty(y.shape, dtype=y.dtype)
-            elif tuple(out.shape) != tuple(y.shape) or out.dtype != y.dtype:
+                out = torch.empty((m, n), dtype=out_dtype)
+            elif tuple(out.shape) != (m, n) or out.dtype != out_dtype:
                 raise ValueError("out must be [M, N] of the output dtype")
-            out.copy_(y, non_blocking=True)
+            # Host tensors: the result (2 bytes per output) is larger than the inputs, so its copy back to the
+            # host dominates.  Rows are processed in blocks and each block's result is copied on a second
+            # stream while the next block is uploaded and multiplied (the two copy directions overlap).
+            blocks = 1 if m < 2 * _HOST_ROW_BLOCK else min(8, m // _HOST_ROW_BLOCK)
+            rows_per = ((m + blocks - 1) // blocks + BLOCK - 1) // BLOCK * BLOCK
+            main = torch.cuda.current_stream()
+            side = _copy_stream(dev)
+            keep = []
+            for r0 in range(0, m, rows_per):
+                r1 = min(m, r0 + rows_per)
+                xr = x[r0:r1].to(dev, non_blocking=True).contiguous()
+                yr = run_rows(xr, None)
+                done = torch.cuda.Event()
+                done.record(main)
+                side.wait_event(done)
+                with torch.cuda.stream(side):
+                    out[r0:r1].copy_(yr, non_blocking=True)
+                keep.append((xr, yr))               # alive until the side stream has finished with them
+            main.wait_stream(side)
             y = out
         status = _read_status(st)[1]               # synchronises: also completes the copy above
         if finite is not None and not bool(finite):
