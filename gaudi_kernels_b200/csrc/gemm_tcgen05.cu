@@ -12,8 +12,16 @@
 //
 // Warp roles (384 threads): warps 0-7 epilogue (two warpgroups; warpgroup w owns output columns
 // 128w..128w+127 of the tile, so it sees a single weight scale per K block), warp 8 TMA producer,
-// warp 9 TMEM owner and MMA issuer (warps 10-11 idle; the third warpgroup gives its registers to the
-// epilogue through setmaxnreg).  The kernel is persistent: one CTA per SM walks a static tile
+// warp 9 TMEM owner and MMA issuer of the even K blocks (TMEM buffer 0), warp 10 MMA issuer of the odd
+// K blocks (buffer 1), warp 11 idle; the third warpgroup gives its registers to the epilogue through
+// setmaxnreg.  One thread needs about 100 cycles more than the tensor pipe to wait, issue four MMAs and
+// commit, so two threads alternate and the pipe stays fed.
+//
+// Barriers, indexed by K block number kb (a running count over the CTA's tiles), four of each so that no
+// waiter can be lapped: `full[kb % 4]` completes when the stage's TMA bytes have landed AND the eight
+// epilogue warps have drained the TMEM buffer kb % 2 of K block kb - 2 (one wait for the MMA issuer);
+// `done[kb % 4]` completes through the issuer's single tcgen05.commit and tells both the epilogue (TMEM
+// buffer ready) and the producer (shared-memory stage free).  The kernel is persistent: one CTA per SM walks a static tile
 // list.  Every barrier wait is bounded; on expiry the CTA raises BFP8_STATUS_WAIT_TIMEOUT and leaves.
 #include <cuda.h>
 
@@ -27,7 +35,7 @@ namespace {
 constexpr int BM = 128;            // tile rows (A rows, TMEM lanes)
 constexpr int BN = 256;            // tile columns (W rows, TMEM columns per buffer)
 constexpr int BK = 128;            // one scale block of K
-constexpr int kStages = 4;
+constexpr int kStages = 4;          // also the number of barrier pairs; the kb % 4 bookkeeping relies on it
 constexpr int kEpiWarps = 8;
 constexpr int kThreads = (kEpiWarps + 4) * 32;   // warps 10, 11 only complete the third warpgroup
 constexpr int kTmemCols = 512;     // two accumulator buffers of BN columns
@@ -39,10 +47,8 @@ constexpr int kOutWarpBytes = 32 * 64 * 2;                  // per warp: one box
 constexpr int kOutStageBytes = kEpiWarps * kOutWarpBytes;
 
 struct SmemTail {
-  uint64_t full[kStages];
-  uint64_t empty[kStages];
-  uint64_t tmem_full[2];
-  uint64_t tmem_empty[2];
+  uint64_t full[kStages];          // TMA bytes of K block kb + release of TMEM buffer kb % 2 by the 8 epilogue warps
+  uint64_t done[kStages];          // MMAs of K block kb complete: TMEM buffer readable, stage reusable
   uint32_t tmem_base;
   uint32_t abort_flag;
 };
@@ -92,12 +98,8 @@ gemm_block128_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
-      ptx::mbar_init(ptx::smem_u32(&tail->full[s]), 1);
-      ptx::mbar_init(ptx::smem_u32(&tail->empty[s]), 1);
-    }
-    for (int b = 0; b < 2; ++b) {
-      ptx::mbar_init(ptx::smem_u32(&tail->tmem_full[b]), 1);
-      ptx::mbar_init(ptx::smem_u32(&tail->tmem_empty[b]), kEpiWarps);
+      ptx::mbar_init(ptx::smem_u32(&tail->full[s]), 1 + kEpiWarps);
+      ptx::mbar_init(ptx::smem_u32(&tail->done[s]), 1);
     }
     tail->abort_flag = 0;
     ptx::fence_mbar_init();
@@ -127,7 +129,7 @@ gemm_block128_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         int tm, tn;
         tile_coords(t, p.tiles_m, p.tiles_n, p.band, tm, tn);
         for (int g = 0; g < G; ++g) {
-          ok = ptx::mbar_wait(ptx::smem_u32(&tail->empty[stage]), phase ^ 1u, abort_flag, p.wait_limit);
+          ok = ptx::mbar_wait(ptx::smem_u32(&tail->done[stage]), phase ^ 1u, abort_flag, p.wait_limit);
           if (!ok) break;
           const uint32_t full = ptx::smem_u32(&tail->full[stage]);
           const uint32_t a_dst = smem_base + stage * kStageBytes;
@@ -138,30 +140,25 @@ gemm_block128_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         }
       }
     }
-  } else if (warp == kEpiWarps + 1) {
-    // ------------------------------------------------------------------ MMA issuer
+  } else if (warp == kEpiWarps + 1 || warp == kEpiWarps + 2) {
+    // ------------------------------------------------------------------ MMA issuers (even / odd K blocks)
     if (lane == 0) {
       constexpr uint32_t idesc = ptx::umma_idesc_e4m3(BM, BN);
-      uint32_t stage = 0, phase = 0, kb = 0;
-      bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        for (int g = 0; g < G; ++g, ++kb) {
-          const uint32_t buf = kb & 1u, acc_phase = (kb >> 1) & 1u;
-          ok = ptx::mbar_wait(ptx::smem_u32(&tail->tmem_empty[buf]), acc_phase ^ 1u, abort_flag, p.wait_limit) &&
-               ptx::mbar_wait(ptx::smem_u32(&tail->full[stage]), phase, abort_flag, p.wait_limit);
-          if (!ok) break;
-          ptx::tc_fence_after_sync();
-          const uint32_t a_addr = smem_base + stage * kStageBytes;
-          const uint64_t a_desc = ptx::umma_desc_k128(a_addr);
-          const uint64_t b_desc = ptx::umma_desc_k128(a_addr + kABytes);
-          const uint32_t d = tmem_base + buf * BN;
+      const uint32_t parity = warp - (kEpiWarps + 1);          // which K blocks, and which TMEM buffer, are mine
+      const uint32_t d = tmem_base + parity * BN;
+      long long total = 0;                                     // K blocks of this CTA
+      for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) total += G;
+      for (long long kb = parity; kb < total; kb += 2) {
+        const uint32_t stage = static_cast<uint32_t>(kb) & (kStages - 1), phase = static_cast<uint32_t>(kb >> 2) & 1u;
+        if (!ptx::mbar_wait(ptx::smem_u32(&tail->full[stage]), phase, abort_flag, p.wait_limit)) break;
+        ptx::tc_fence_after_sync();
+        const uint32_t a_addr = smem_base + stage * kStageBytes;
+        const uint64_t a_desc = ptx::umma_desc_k128(a_addr);
+        const uint64_t b_desc = ptx::umma_desc_k128(a_addr + kABytes);
 #pragma unroll
-          for (int k4 = 0; k4 < BK / 32; ++k4)   // +32 bytes along K = +2 in the descriptor's address field
-            ptx::umma_f8(d, a_desc + 2u * k4, b_desc + 2u * k4, idesc, k4 > 0);
-          ptx::umma_commit(ptx::smem_u32(&tail->empty[stage]));
-          ptx::umma_commit(ptx::smem_u32(&tail->tmem_full[buf]));
-          if (++stage == kStages) { stage = 0; phase ^= 1u; }
-        }
+        for (int k4 = 0; k4 < BK / 32; ++k4)   // +32 bytes along K = +2 in the descriptor's address field
+          ptx::umma_f8(d, a_desc + 2u * k4, b_desc + 2u * k4, idesc, k4 > 0);
+        ptx::umma_commit(ptx::smem_u32(&tail->done[stage]));
       }
     }
    }
@@ -177,6 +174,11 @@ gemm_block128_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     uint8_t* my_stage = out_stage + warp * kOutWarpBytes;
     uint32_t kb = 0;
     bool ok = true;
+    // the first use of either TMEM buffer has nothing to wait for
+    if (lane == 0) {
+      ptx::mbar_arrive(ptx::smem_u32(&tail->full[0]));
+      ptx::mbar_arrive(ptx::smem_u32(&tail->full[1]));
+    }
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
       int tm, tn;
       tile_coords(t, p.tiles_m, p.tiles_n, p.band, tm, tn);
@@ -196,8 +198,8 @@ gemm_block128_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       float sa1 = (live && G > 1) ? __ldg(sa_ptr + p.ldsa) : 0.0f, sw1 = (live && G > 1) ? __ldg(sw_ptr + 1) : 0.0f;
       uint32_t ra[32], rb[32];
       {
-        const uint32_t buf = kb & 1u, acc_phase = (kb >> 1) & 1u;
-        ok = ptx::mbar_wait(ptx::smem_u32(&tail->tmem_full[buf]), acc_phase, abort_flag, p.wait_limit);
+        const uint32_t buf = kb & 1u;
+        ok = ptx::mbar_wait(ptx::smem_u32(&tail->done[kb & (kStages - 1)]), (kb >> 2) & 1u, abort_flag, p.wait_limit);
         if (!ok) break;
         ptx::tc_fence_after_sync();
         const uint32_t taddr = tmem_base + lane_addr + buf * BN + wg * 128;
@@ -233,7 +235,7 @@ gemm_block128_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         // every column of this buffer is in registers: hand it back to the MMA warp
         ptx::tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&tail->tmem_empty[buf]));
+        if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&tail->full[(kb + 2) & (kStages - 1)]));
         {
 #pragma unroll
           for (int j = 0; j < 16; ++j)
@@ -244,8 +246,8 @@ gemm_block128_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         }
         if (g + 1 < G) {
           // first half of the next K block's buffer
-          const uint32_t nkb = kb + 1, nbuf = nkb & 1u, nphase = (nkb >> 1) & 1u;
-          ok = ptx::mbar_wait(ptx::smem_u32(&tail->tmem_full[nbuf]), nphase, abort_flag, p.wait_limit);
+          const uint32_t nkb = kb + 1, nbuf = nkb & 1u;
+          ok = ptx::mbar_wait(ptx::smem_u32(&tail->done[nkb & (kStages - 1)]), (nkb >> 2) & 1u, abort_flag, p.wait_limit);
           if (!ok) break;
           ptx::tc_fence_after_sync();
             const uint32_t naddr = tmem_base + lane_addr + nbuf * BN + wg * 128;
