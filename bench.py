@@ -222,6 +222,51 @@ def bench_codec(torch, lib, device, steps, warmup):
     return out
 
 
+def bench_decode_bucket(torch, lib, device, k=4096, n=14336, reps=20, rounds=8):
+    """Small-M GEMM (the decode bucket) at one weight shape: HBM-bound on the 58.7 MB of weight codes.
+
+    The weight fits in L2, so launches rotate over four weight copies; `reps` launches are captured in one CUDA
+    graph (host launch latency is longer than the kernel) and the graph is timed with CUDA events.
+    """
+    g = torch.Generator(device=device).manual_seed(3)
+    ws_codes = [torch.randint(0, 0x77, (n, k), generator=g, device=device, dtype=torch.uint8) for _ in range(4)]
+    w_scales = torch.rand((n // 128, k // 128), generator=g, device=device) * 1e-3
+    status = torch.zeros(4, dtype=torch.int32, device=device)
+    out = {}
+    for m in (1, 8, 32, 64):
+        a_codes = torch.randint(0, 0x77, (m, k), generator=g, device=device, dtype=torch.uint8)
+        a_scales = torch.rand((k // 128, m), generator=g, device=device)
+        y = torch.empty((m, n), dtype=torch.bfloat16, device=device)
+        ws_bytes = lib.bfp8_gemm_block128_workspace_bytes(m, n, k)
+        ws = torch.zeros(ws_bytes, dtype=torch.uint8, device=device)
+
+        def launch(count):
+            stream = torch.cuda.current_stream().cuda_stream
+            for i in range(count):
+                rc = lib.bfp8_gemm_block128(a_codes.data_ptr(), k, a_scales.data_ptr(), m, ws_codes[i % 4].data_ptr(), k,
+                                            w_scales.data_ptr(), None, y.data_ptr(), 1, n, m, n, k, ws.data_ptr(), ws_bytes,
+                                            status.data_ptr() + 8, stream)
+                assert rc == 0, rc
+
+        launch(4)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            launch(reps)
+        ts = []
+        for _ in range(rounds):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1) / reps)
+        us = statistics.median(ts) * 1e3
+        nbytes = n * k + 4 * (n // 128) * (k // 128) + m * k + 4 * m * (k // 128) + 2 * m * n
+        out["M=%d" % m] = {"us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1), "tflops": round(2.0 * m * n * k / us / 1e6, 1)}
+    return out
+
+
 def make_problem(torch, gk, m, k, n_local, n_offset, n_total, device, seed=0):
     """Synthetic operands: bf16 activations and an fp32 weight slice, quantized on the GPU by the library."""
     g = torch.Generator(device="cpu").manual_seed(seed)
@@ -430,7 +475,8 @@ def main():
                "d2h_bytes_per_step": yh.numel() * 2 + 16,
                "call": "gaudi_kernels_b200.reference(x, weight, scales, native_half=True) on pinned host tensors: "
                        "H2D, re-encode, 1x128 quantize, GEMM, D2H",
-               "gpu_launches_per_step": 3}
+               # one weight re-encode, then a 1x128 quantize and a GEMM per pipelined row block
+               "gpu_launches_per_step": 1 + 2 * (1 if m < 2048 else min(8, m // 1024))}
 
     if rank != 0:
         if world > 1:
@@ -464,6 +510,11 @@ def main():
         codec = bench_codec(torch, lib, device, 8, 3)
         line["codec_hbm_gbs"] = {k: round(v["gbs"], 1) for k, v in codec.items()}
         line["codec_hbm_frac_of_measured"] = {k: round(v["gbs"] / hbm_gbs, 3) for k, v in codec.items()}
+        for dk, dn in ((4096, 14336), (14336, 4096)):
+            decode = bench_decode_bucket(torch, lib, device, dk, dn)
+            for v in decode.values():
+                v["hbm_frac_of_measured"] = round(v["gbs"] / hbm_gbs, 3)
+            line["decode_bucket_k%d_n%d" % (dk, dn)] = decode
     if gather is not None:
         line["gather"] = gather
     if e2e is not None:

@@ -351,6 +351,62 @@ quant_act_token_kernel(const uint16_t* __restrict__ x, int64_t k, int64_t ldx, u
   }
 }
 
+// Rows of up to 4096 columns: one warp per row, all 16 of a lane's 16-byte loads in flight before the first use,
+// and no CTA-wide barrier between the maximum and the conversion.  Same arithmetic as the CTA-per-row kernel.
+constexpr int kTokWarpVecs = 16;
+constexpr int kTokWarpMaxK = kTokWarpVecs * 32 * 8;
+constexpr int kTokWarpThreads = 128;    // four rows per CTA; three CTAs fit one SM's registers
+
+__global__ void __launch_bounds__(kTokWarpThreads, 3)
+quant_act_token_warp_kernel(const uint16_t* __restrict__ x, int64_t m, int64_t k, int64_t ldx,
+                            uint8_t* __restrict__ codes, int64_t ld_codes, float* __restrict__ scales,
+                            int native_half, uint32_t* __restrict__ status) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * (kTokWarpThreads / 32) + (threadIdx.x >> 5);
+  if (row >= m) return;
+  const uint4* xrow = reinterpret_cast<const uint4*>(x + row * ldx);
+  uint2* crow = reinterpret_cast<uint2*>(codes + row * ld_codes);
+  const int nvec = static_cast<int>(k >> 3);
+  uint4 raw[kTokWarpVecs];
+#pragma unroll
+  for (int u = 0; u < kTokWarpVecs; ++u) {
+    const int i = u * 32 + lane;
+    raw[u] = make_uint4(0u, 0u, 0u, 0u);
+    if (i < nvec) raw[u] = __ldcs(xrow + i);
+  }
+  float amax = 0.0f;
+#pragma unroll
+  for (int u = 0; u < kTokWarpVecs; ++u) {
+    const uint32_t* r = reinterpret_cast<const uint32_t*>(&raw[u]);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) amax = max_abs_nan(max_abs_nan(amax, bf16_lo_to_float(r[j])), bf16_hi_to_float(r[j]));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = max_abs_nan(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if (!(amax < __int_as_float(0x7f800000)) && lane == 0 && status != nullptr)
+    atomicOr(status, BFP8_STATUS_NONFINITE_INPUT);
+  const float s = __fdiv_rn(amax == 0.0f ? 1.0f : amax, 448.0f);
+  const float rcp = __frcp_rn(s);
+  if (lane == 0) scales[row] = native_half ? __fmul_rn(s, 2.0f) : s;
+#pragma unroll
+  for (int u = 0; u < kTokWarpVecs; ++u) {
+    const int i = u * 32 + lane;
+    const uint32_t* r = reinterpret_cast<const uint32_t*>(&raw[u]);
+    float f[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { f[2 * j] = bf16_lo_to_float(r[j]); f[2 * j + 1] = bf16_hi_to_float(r[j]); }
+    uint2 q;
+    if (native_half) {
+      q.x = quant_half_e4m3x4(f[0], f[1], f[2], f[3], s, rcp);
+      q.y = quant_half_e4m3x4(f[4], f[5], f[6], f[7], s, rcp);
+    } else {
+      q.x = quant_e4m3x4(f[0], f[1], f[2], f[3], s, rcp);
+      q.y = quant_e4m3x4(f[4], f[5], f[6], f[7], s, rcp);
+    }
+    if (i < nvec) __stcs(crow + i, q);
+  }
+}
+
 // ---------------------------------------------------------------------------------------------
 // K4  decode: value(code) * block scale.  A thread turns 4 codes (one 32-bit load) into one
 //     16-byte (fp32) or 8-byte (bf16) store, so both sides of every warp access are contiguous.
@@ -533,8 +589,15 @@ extern "C" int bfp8_quant_act_token_bf16(const uint16_t* x, int64_t m, int64_t k
   if (m <= 0 || k <= 0 || ldx < k || ld_codes < k || m > 2147483647LL) return BFP8_ERR_SHAPE;
   if (!aligned(x, 2) || !aligned(scales, 4)) return BFP8_ERR_ALIGN;
   const int vec = aligned(x, 16) && aligned(codes, 8) && ldx % 8 == 0 && ld_codes % 8 == 0 && k % 8 == 0;
-  quant_act_token_kernel<<<static_cast<int>(m), kTokThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      x, k, ldx, codes, ld_codes, scales, native_half, vec, status_dev);
+  if (vec && k <= kTokWarpMaxK) {
+    const int rows_per_cta = kTokWarpThreads / 32;
+    quant_act_token_warp_kernel<<<static_cast<int>((m + rows_per_cta - 1) / rows_per_cta), kTokWarpThreads, 0,
+                                  static_cast<cudaStream_t>(stream)>>>(x, m, k, ldx, codes, ld_codes, scales,
+                                                                       native_half, status_dev);
+  } else {
+    quant_act_token_kernel<<<static_cast<int>(m), kTokThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        x, k, ldx, codes, ld_codes, scales, native_half, vec, status_dev);
+  }
   BFP8_CUDA_TRY(cudaGetLastError());
   return BFP8_OK;
 }

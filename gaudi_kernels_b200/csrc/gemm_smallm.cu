@@ -170,23 +170,25 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     }
   } else if (warp == kEpiWarps + 2) {
     // ------------------------------------------------------------------ scale loader
-    constexpr int kPer = (MP + 31) / 32;                         // scale products per lane and unit
-    float v[kScaleAhead][kPer];
+    constexpr int kPer = (MP + 31) / 32;                         // activation scales per lane and unit
+    // Raw scales of the next kScaleAhead units.  They are multiplied only when their unit comes up: using a
+    // loaded value right away would stall this warp for a full L2 round trip on every unit.
+    float va[kScaleAhead][kPer], vw[kScaleAhead];
     int f_tile = static_cast<int>(u0 / G), f_g = static_cast<int>(u0 % G);   // unit the next fetch belongs to
-    auto fetch = [&](long long, float (&dst)[kPer]) {
+    auto fetch = [&](float (&dst)[kPer], float& sw) {
       const int tile = f_tile, g = f_g;
       if (++f_g == G) { f_g = 0; ++f_tile; }
-      const float sw = __ldg(p.w_scales + static_cast<int64_t>(tile) * G + g);
+      sw = __ldg(p.w_scales + static_cast<int64_t>(tile) * G + g);
       const float* sa = p.a_scales + static_cast<int64_t>(g) * p.ldsa;
 #pragma unroll
       for (int q = 0; q < kPer; ++q) {
         const int i = lane + 32 * q;
-        dst[q] = (i < p.m) ? __ldg(sa + i) * sw : 0.0f;
+        dst[q] = (i < p.m) ? __ldg(sa + i) : 0.0f;
       }
     };
 #pragma unroll
     for (int i = 0; i < kScaleAhead; ++i)
-      if (u0 + i < u1) fetch(u0 + i, v[i]);
+      if (u0 + i < u1) fetch(va[i], vw[i]);
     uint32_t kb = 0;
     bool ok = true;
     for (long long base = u0; base < u1 && ok; base += kScaleAhead) {
@@ -199,10 +201,10 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
           if (ok) {
 #pragma unroll
             for (int q = 0; q < kPer; ++q)
-              if (lane + 32 * q < MP) tail->scale[buf][lane + 32 * q] = v[i][q];
+              if (lane + 32 * q < MP) tail->scale[buf][lane + 32 * q] = va[i][q] * vw[i];
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&tail->scale_full[buf]));
-            if (u + kScaleAhead < u1) fetch(u + kScaleAhead, v[i]);
+            if (u + kScaleAhead < u1) fetch(va[i], vw[i]);
             ++kb;
           }
         }
