@@ -36,6 +36,9 @@ SIGNATURES = {
                                        _i64, _i64, _i64, _ptr, _ptr]),
     "bfp8_gemm_block128_noalloc": (_int, [_ptr, _i64, _ptr, _i64, _ptr, _i64, _ptr, _ptr, _ptr, _int, _i64,
                                           _i64, _i64, _i64, _ptr, _ptr]),
+    "bfp8_swiglu_interleave_weight": (_int, [_ptr, _i64, _ptr, _i64, _i64, _i64, _ptr]),
+    "bfp8_gemm_block128_swiglu": (_int, [_ptr, _i64, _ptr, _i64, _ptr, _i64, _ptr, _ptr, _ptr, _i64,
+                                         _i64, _i64, _i64, _ptr, _ptr]),
 }
 
 _lib = None

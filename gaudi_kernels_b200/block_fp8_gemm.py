@@ -192,6 +192,77 @@ def prepare_weight(weight, scales, native_half=True):
     return weight, scales
 
 
+def prepare_weight_swiglu(weight, scales, native_half=True):
+    """Load-time preparation of a fused gate/up weight for gemm_block_fp8_swiglu.
+
+    weight float8_e4m3fn / uint8 [2 * I, K] with the gate projection in rows [0, I) and the up projection in
+    rows [I, 2 * I) (the order csrc/tpc/generic_dense/silu_and_mul_bf16.c:29 reads); scales fp32 [2 * I / 128, G].
+    Re-encodes to the half range when asked (as prepare_weight), then interleaves the rows in chunks of 64
+    so a GEMM tile holds both factors of its outputs.  The scale grid keeps its order.  I % 128 == 0.
+    """
+    codes, scales = prepare_weight(weight, scales, native_half)
+    if codes.ndim != 2 or codes.shape[0] % (2 * BLOCK) != 0:
+        raise ValueError("fused gate/up weight must be [2 * I, K] with I a multiple of 128")
+    inter, k = codes.shape[0] // 2, codes.shape[1]
+    dev = codes.device
+    lib = _lib.load()
+    with torch.cuda.device(dev):
+        src = codes.contiguous().view(torch.uint8)
+        if k % 16 != 0:
+            src = torch.nn.functional.pad(src, (0, (k + 15) // 16 * 16 - k))
+        dst = torch.empty_like(src)
+        rc = lib.bfp8_swiglu_interleave_weight(src.data_ptr(), src.stride(0), dst.data_ptr(), dst.stride(0), inter,
+                                               src.shape[1], _stream_ptr())
+        _lib.check(rc, "bfp8_swiglu_interleave_weight")
+    return dst.view(torch.float8_e4m3fn), scales
+
+
+def gemm_block_fp8_swiglu(a_codes, a_scales, w_codes, w_scales, bias=None, out=None, check=True):
+    """bf16 [M, I] = silu(gate) * up, with gate | up = the block-scaled GEMM of gemm_block_fp8 rounded to bf16.
+
+    The gate/up GEMM and gk_silu_and_mul_bf16_v1 (csrc/tpc/generic_dense/silu_and_mul_bf16.c:16) as one
+    kernel.  w_codes [2 * I, K'] and w_scales [2 * I / 128, G] come from prepare_weight_swiglu (K' is K
+    rounded up to 16); bias fp32 [2 * I] in the fused weight's original order, or None.
+    """
+    for name, t in (("a_codes", a_codes), ("w_codes", w_codes)):
+        if (not isinstance(t, torch.Tensor) or t.dtype not in (torch.float8_e4m3fn, torch.uint8) or t.ndim != 2
+                or not t.is_contiguous() or t.device.type != "cuda"):
+            raise ValueError("%s must be a contiguous 2-D E4M3 tensor on a CUDA device" % name)
+    m, k = a_codes.shape
+    n2 = w_codes.shape[0]
+    if n2 % (2 * BLOCK) != 0 or m < 1 or k < 1 or w_codes.shape[1] != (k + 15) // 16 * 16:
+        raise ValueError("w_codes must be the [2 * I, K] output of prepare_weight_swiglu, I a multiple of 128")
+    inter = n2 // 2
+    g = (k + BLOCK - 1) // BLOCK
+    if (not isinstance(w_scales, torch.Tensor) or w_scales.dtype != torch.float32 or not w_scales.is_contiguous()
+            or tuple(w_scales.shape) != (n2 // BLOCK, g)):
+        raise ValueError("original block128 scale grid mismatch")
+    dev = a_codes.device
+    if bias is not None:
+        if bias.numel() != n2:
+            raise ValueError("bias with 2 * I elements required")
+        bias = bias.to(device=dev, dtype=torch.float32).contiguous().view(-1)
+    lib = _lib.load()
+    with torch.cuda.device(dev):
+        if k % 16 != 0:
+            a_codes = torch.nn.functional.pad(a_codes.view(torch.uint8), (0, w_codes.shape[1] - k))
+        sa, ldsa = _group_major(a_scales.to(dev), m, g)
+        w_scales = w_scales.to(dev)
+        if out is None:
+            out = torch.empty((m, inter), dtype=torch.bfloat16, device=dev)
+        elif (out.dtype != torch.bfloat16 or tuple(out.shape) != (m, inter) or out.stride(1) != 1 or out.device != dev):
+            raise ValueError("out must be bf16 [M, I] with unit column stride on the operand device")
+        st = _status_buffer(dev)
+        rc = lib.bfp8_gemm_block128_swiglu(
+            a_codes.data_ptr(), a_codes.stride(0), sa.data_ptr(), ldsa, w_codes.data_ptr(), w_codes.stride(0),
+            w_scales.data_ptr(), bias.data_ptr() if bias is not None else None, out.data_ptr(), out.stride(0),
+            m, inter, w_codes.shape[1], st.data_ptr() + 8, _stream_ptr())
+        _lib.check(rc, "bfp8_gemm_block128_swiglu")
+        if check and _read_status(st)[1] & _lib.STATUS_WAIT_TIMEOUT:
+            raise _lib.Bfp8Error(_WAIT_TIMEOUT_MSG)
+    return out
+
+
 def reference(x, weight, scales, *, native_half=False, bias=None, out_dtype=torch.bfloat16, out=None):
     """Drop-in for gaudi_kernels.block_fp8_oracle.reference, computed on the GPU.
 

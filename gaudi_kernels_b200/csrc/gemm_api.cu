@@ -5,7 +5,7 @@ namespace bfp8 {
 int launch_gemm_large(const uint8_t* a_codes, int64_t lda, const float* a_scales, int64_t ldsa,
                       const uint8_t* w_codes, int64_t ldw, const float* w_scales, const float* bias, void* out,
                       int out_dtype, int64_t ldo, int64_t m, int64_t n, int64_t k, uint32_t* status_dev,
-                      long long wait_limit, int max_ctas, int band, cudaStream_t st);
+                      long long wait_limit, int max_ctas, int band, int inter, cudaStream_t st);
 int launch_gemm_pair(const uint8_t* a_codes, int64_t lda, const float* a_scales, int64_t ldsa,
                      const uint8_t* w_codes, int64_t ldw, const float* w_scales, const float* bias, void* out,
                      int out_dtype, int64_t ldo, int64_t m, int64_t n, int64_t k, uint32_t* status_dev,
@@ -70,7 +70,7 @@ extern "C" int bfp8_gemm_block128_ex(const uint8_t* a_codes, int64_t lda, const 
     return launch_gemm_pair(a_codes, lda, a_scales, ldsa, w_codes, ldw, w_scales, bias, out, out_dtype, ldo, m, n, k,
                             status_dev, limit, max_ctas, st);
   return launch_gemm_large(a_codes, lda, a_scales, ldsa, w_codes, ldw, w_scales, bias, out, out_dtype, ldo, m, n, k,
-                           status_dev, limit, max_ctas, /*band=*/0, st);
+                           status_dev, limit, max_ctas, /*band=*/0, /*inter=*/0, st);
 }
 
 extern "C" int bfp8_gemm_block128(const uint8_t* a_codes, int64_t lda, const float* a_scales, int64_t ldsa,
@@ -97,4 +97,60 @@ extern "C" int bfp8_gemm_token_channel(const uint8_t* a_codes, int64_t lda, cons
   if (out_dtype == BFP8_OUT_F32 && !aligned(out, 4)) return BFP8_ERR_ALIGN;
   return launch_gemm_channel(a_codes, lda, a_scales, w_codes, ldw, w_scales, bias, out, out_dtype, ldo, m, n, k,
                              status_dev, kDefaultWaitLimit, 0, static_cast<cudaStream_t>(stream));
+}
+
+// ---- gate/up GEMM with the SwiGLU step fused into its epilogue ---------------------------------------
+
+namespace {
+constexpr int kSwigluChunk = 64;
+
+// Rows [0, inter) of src are the gate projection, rows [inter, 2 inter) the up projection.  Chunk c of 64
+// outputs becomes dst rows [128 c, 128 c + 64) (gate) and [128 c + 64, 128 c + 128) (up).  16 bytes per thread.
+__global__ void __launch_bounds__(256)
+swiglu_interleave_kernel(const uint8_t* __restrict__ src, int64_t ld_src, uint8_t* __restrict__ dst, int64_t ld_dst,
+                         int64_t inter, int64_t vecs_per_row) {
+  const int64_t total = 2 * inter * vecs_per_row;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t r = i / vecs_per_row, v = i - r * vecs_per_row;          // destination row, 16-byte column
+    const int64_t chunk = r / (2 * kSwigluChunk), in_chunk = r - chunk * 2 * kSwigluChunk;
+    const int64_t s_row = in_chunk < kSwigluChunk ? chunk * kSwigluChunk + in_chunk
+                                                  : inter + chunk * kSwigluChunk + (in_chunk - kSwigluChunk);
+    const uint4 x = __ldcs(reinterpret_cast<const uint4*>(src + s_row * ld_src) + v);
+    __stcs(reinterpret_cast<uint4*>(dst + r * ld_dst) + v, x);
+  }
+}
+}  // namespace
+
+extern "C" int bfp8_swiglu_interleave_weight(const uint8_t* w_codes, int64_t ld_src, uint8_t* out, int64_t ld_dst,
+                                             int64_t inter, int64_t k, void* stream) {
+  if (!w_codes || !out) return BFP8_ERR_NULL;
+  if (inter <= 0 || k <= 0 || ld_src < k || ld_dst < k || inter > (1 << 29)) return BFP8_ERR_SHAPE;
+  if (inter % 128 != 0) return BFP8_ERR_UNSUPPORTED;
+  if (k % 16 != 0 || ld_src % 16 != 0 || ld_dst % 16 != 0 || !aligned(w_codes, 16) || !aligned(out, 16))
+    return BFP8_ERR_ALIGN;
+  if (w_codes == out) return BFP8_ERR_SHAPE;                       // not an in-place operation
+  const int64_t vecs = k / 16, total = 2 * inter * vecs;
+  const int64_t want = (total + 255) / 256;
+  const int grid = static_cast<int>(want < static_cast<int64_t>(sm_count()) * 16 ? want : static_cast<int64_t>(sm_count()) * 16);
+  swiglu_interleave_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(w_codes, ld_src, out, ld_dst, inter, vecs);
+  BFP8_CUDA_TRY(cudaGetLastError());
+  return BFP8_OK;
+}
+
+extern "C" int bfp8_gemm_block128_swiglu(const uint8_t* a_codes, int64_t lda, const float* a_scales, int64_t ldsa,
+                                         const uint8_t* w_codes, int64_t ldw, const float* w_scales,
+                                         const float* bias, void* out, int64_t ldo,
+                                         int64_t m, int64_t inter, int64_t k, uint32_t* status_dev, void* stream) {
+  if (!a_codes || !a_scales || !w_codes || !w_scales || !out || !status_dev) return BFP8_ERR_NULL;
+  if (m <= 0 || inter <= 0 || k <= 0 || m > (1 << 30) || inter > (1 << 29) || k > (1 << 30)) return BFP8_ERR_SHAPE;
+  if (lda < k || ldw < k || ldo < inter || ldsa < m) return BFP8_ERR_SHAPE;
+  if (inter % 128 != 0) return BFP8_ERR_UNSUPPORTED;               // gate / up boundary on a scale-block boundary
+  if (!aligned(a_codes, 16) || !aligned(w_codes, 16) || lda % 16 != 0 || ldw % 16 != 0) return BFP8_ERR_ALIGN;
+  if (!aligned(a_scales, 4) || !aligned(w_scales, 4) || !aligned(status_dev, 4)) return BFP8_ERR_ALIGN;
+  if (bias && !aligned(bias, 4)) return BFP8_ERR_ALIGN;
+  if (!aligned(out, 16) || ldo % 8 != 0) return BFP8_ERR_ALIGN;
+  return launch_gemm_large(a_codes, lda, a_scales, ldsa, w_codes, ldw, w_scales, bias, out, BFP8_OUT_BF16, ldo,
+                           m, 2 * inter, k, status_dev, kDefaultWaitLimit, 0, /*band=*/0, static_cast<int>(inter),
+                           static_cast<cudaStream_t>(stream));
 }

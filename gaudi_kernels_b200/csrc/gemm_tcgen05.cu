@@ -64,6 +64,7 @@ struct GemmParams {
   int m, n, k, groups;
   int tiles_m, tiles_n;
   int band;                // tile-rows per band of the tile walk
+  int inter;               // SwiGLU only: width of the gate and of the up projection (N = 2 * inter)
   long long wait_limit;
   uint32_t* status;
 };
@@ -80,7 +81,18 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
   tn = r / rows;
 }
 
-template <bool kOutBf16>
+// silu(g) * u as csrc/tpc/generic_dense/silu_and_mul_bf16.c:4-13 defines it: g / (1 + exp(-g)), exactly 0 for
+// g <= -88, NaN passed through.  The fast division flushes quotients below 2^-126 (g in (-88, -87.3)) to zero.
+__device__ __forceinline__ float silu_mul(float g, float u) {
+  const float q = __fdividef(g, 1.0f + __expf(-g));
+  return (g <= -88.0f ? 0.0f : q) * u;
+}
+
+// kSwiGLU: W holds gate and up rows interleaved in chunks of 64 (bfp8_swiglu_interleave_weight), so the 128
+// tile columns of a warpgroup are 64 gate columns followed by the 64 up columns of the same outputs, and a
+// thread ends a tile holding both factors of its 64 outputs.  The tile's 256 weight rows are outputs
+// 128 tn .. 128 tn + 127, which lie in one scale block of the gate grid and one of the up grid.
+template <bool kOutBf16, bool kSwiGLU>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_block128_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
                      const __grid_constant__ CUtensorMap tmap_out, const GemmParams p) {
@@ -183,12 +195,15 @@ gemm_block128_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       int tm, tn;
       tile_coords(t, p.tiles_m, p.tiles_n, p.band, tm, tn);
       const int row = tm * BM + quad * 32 + lane;
-      const int col0 = tn * BN + wg * 128;
+      // first output column of this thread: 128 of the tile's 256, or with SwiGLU 64 of its 128 outputs
+      const int col0 = kSwiGLU ? tn * 128 + wg * 64 : tn * BN + wg * 128;
       const bool row_ok = row < p.m;
-      const int nb = col0 >> 7;
-      const bool live = row_ok && col0 < p.n;
+      const int nb = kSwiGLU ? tn : col0 >> 7;
+      const bool live = row_ok && (kSwiGLU || col0 < p.n);
       const float* sa_ptr = p.a_scales + row;
       const float* sw_ptr = p.w_scales + static_cast<int64_t>(nb) * G;
+      // SwiGLU: scale row of the up projection's block (the grid lists the gate blocks first)
+      const float* su_ptr = p.w_scales + static_cast<int64_t>((p.inter >> 7) + nb) * G;
       float2 acc[64];
 #pragma unroll
       for (int j = 0; j < 64; ++j) acc[j] = make_float2(0.0f, 0.0f);
@@ -196,6 +211,11 @@ gemm_block128_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       // so no load is waited for at the top of the loop
       float sa0 = live ? __ldg(sa_ptr) : 0.0f, sw0 = live ? __ldg(sw_ptr) : 0.0f;
       float sa1 = (live && G > 1) ? __ldg(sa_ptr + p.ldsa) : 0.0f, sw1 = (live && G > 1) ? __ldg(sw_ptr + 1) : 0.0f;
+      float su0 = 0.0f, su1 = 0.0f;
+      if (kSwiGLU) {
+        su0 = live ? __ldg(su_ptr) : 0.0f;
+        su1 = (live && G > 1) ? __ldg(su_ptr + 1) : 0.0f;
+      }
       uint32_t ra[32], rb[32];
       {
         const uint32_t buf = kb & 1u;
@@ -207,15 +227,18 @@ gemm_block128_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         ptx::tmem_ld32(taddr + 32, rb);
       }
       for (int g = 0; g < G; ++g, ++kb) {
-        float sa2 = 0.0f, sw2 = 0.0f;
+        float sa2 = 0.0f, sw2 = 0.0f, su2 = 0.0f;
         if (live && g + 2 < G) {
           sa2 = __ldg(sa_ptr + static_cast<int64_t>(g + 2) * p.ldsa);
           sw2 = __ldg(sw_ptr + g + 2);
+          if (kSwiGLU) su2 = __ldg(su_ptr + g + 2);
         }
         const uint32_t buf = kb & 1u;
         const uint32_t taddr = tmem_base + lane_addr + buf * BN + wg * 128;
         const float s = sa0 * sw0;
         const float2 sv = make_float2(s, s);
+        const float s_up = kSwiGLU ? sa0 * su0 : s;            // columns 64..127 of the warpgroup
+        const float2 sv_up = make_float2(s_up, s_up);
         ptx::tmem_wait_ld32(ra);
         ptx::tmem_regs_ready32(rb);
         {
@@ -239,10 +262,10 @@ gemm_block128_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         {
 #pragma unroll
           for (int j = 0; j < 16; ++j)
-            acc[32 + j] = __ffma2_rn(make_float2(__uint_as_float(ra[2 * j]), __uint_as_float(ra[2 * j + 1])), sv, acc[32 + j]);
+            acc[32 + j] = __ffma2_rn(make_float2(__uint_as_float(ra[2 * j]), __uint_as_float(ra[2 * j + 1])), sv_up, acc[32 + j]);
 #pragma unroll
           for (int j = 0; j < 16; ++j)
-            acc[48 + j] = __ffma2_rn(make_float2(__uint_as_float(rb[2 * j]), __uint_as_float(rb[2 * j + 1])), sv, acc[48 + j]);
+            acc[48 + j] = __ffma2_rn(make_float2(__uint_as_float(rb[2 * j]), __uint_as_float(rb[2 * j + 1])), sv_up, acc[48 + j]);
         }
         if (g + 1 < G) {
           // first half of the next K block's buffer
@@ -256,9 +279,47 @@ gemm_block128_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         }
         sa0 = sa1; sw0 = sw1;
         sa1 = sa2; sw1 = sw2;
+        if (kSwiGLU) { su0 = su1; su1 = su2; }
       }
       if (!ok) break;
       // ---- tile done: bias, rounding, store
+      if (kSwiGLU) {
+        // gate and up are rounded to bf16 as the unfused GEMM would store them, then silu(gate) * up is
+        // formed in fp32 and rounded once (silu_and_mul_bf16.c:16); one box of 32 rows x 64 outputs per warp
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          float2 gt = acc[j], up = acc[32 + j];
+          if (p.bias != nullptr) {
+            gt.x += __ldg(p.bias + col0 + 2 * j);
+            gt.y += __ldg(p.bias + col0 + 2 * j + 1);
+            up.x += __ldg(p.bias + p.inter + col0 + 2 * j);
+            up.y += __ldg(p.bias + p.inter + col0 + 2 * j + 1);
+          }
+          const uint32_t gp = pack_bf16x2(gt.x, gt.y), upk = pack_bf16x2(up.x, up.y);
+          acc[j] = make_float2(silu_mul(bf16_lo_to_float(gp), bf16_lo_to_float(upk)),
+                               silu_mul(bf16_hi_to_float(gp), bf16_hi_to_float(upk)));
+        }
+        if (lane == 0) ptx::tma_store_wait_read_all();
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int e = j * 4;
+          uint4 v;
+          v.x = pack_bf16x2(acc[e + 0].x, acc[e + 0].y);
+          v.y = pack_bf16x2(acc[e + 1].x, acc[e + 1].y);
+          v.z = pack_bf16x2(acc[e + 2].x, acc[e + 2].y);
+          v.w = pack_bf16x2(acc[e + 3].x, acc[e + 3].y);
+          *reinterpret_cast<uint4*>(my_stage + lane * 128 + ((j ^ (lane & 7)) << 4)) = v;
+        }
+        ptx::fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          const int y = tm * BM + quad * 32;
+          if (y < p.m) ptx::tma_store_2d(&tmap_out, ptx::smem_u32(my_stage), col0, y);
+          ptx::tma_store_commit();
+        }
+        continue;
+      }
       if (p.bias != nullptr) {
 #pragma unroll
         for (int j = 0; j < 64; ++j) {
@@ -362,7 +423,8 @@ int make_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* bas
 int launch_gemm_large(const uint8_t* a_codes, int64_t lda, const float* a_scales, int64_t ldsa,
                       const uint8_t* w_codes, int64_t ldw, const float* w_scales, const float* bias, void* out,
                       int out_dtype, int64_t ldo, int64_t m, int64_t n, int64_t k, uint32_t* status_dev,
-                      long long wait_limit, int max_ctas, int band, cudaStream_t st) {
+                      long long wait_limit, int max_ctas, int band, int inter, cudaStream_t st) {
+  // inter > 0 selects the SwiGLU epilogue: W has n = 2 * inter interleaved rows and the output is [m, inter] bf16
   alignas(64) CUtensorMap tmap_a, tmap_w, tmap_out;
   int rc = make_tensor_map_2d(&tmap_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, a_codes, k, m, lda, BK, BM);
   if (rc != BFP8_OK) return rc;
@@ -370,7 +432,7 @@ int launch_gemm_large(const uint8_t* a_codes, int64_t lda, const float* a_scales
   if (rc != BFP8_OK) return rc;
   const bool bf16 = out_dtype == BFP8_OUT_BF16;
   if (bf16) {
-    rc = make_tensor_map_2d(&tmap_out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, out, n, m, ldo * 2, 64, 32);
+    rc = make_tensor_map_2d(&tmap_out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, out, inter > 0 ? inter : n, m, ldo * 2, 64, 32);
     if (rc != BFP8_OK) return rc;
   } else {
     tmap_out = tmap_a;   // unused on the fp32 path
@@ -391,13 +453,16 @@ int launch_gemm_large(const uint8_t* a_codes, int64_t lda, const float* a_scales
   p.wait_limit = wait_limit;
   p.status = status_dev;
   p.band = band > 0 ? band : 16;
+  p.inter = inter;
   const int tiles = p.tiles_m * p.tiles_n;
   int grid = sm_count();
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   if (tiles < grid) grid = tiles;
-  auto kern = bf16 ? gemm_block128_kernel<true> : gemm_block128_kernel<false>;
-  static bool done[2][64] = {};
-  rc = ensure_smem_limit(kern, kSmemBytes, done[bf16 ? 1 : 0]);
+  if (inter > 0 && !bf16) return BFP8_ERR_UNSUPPORTED;
+  auto kern = inter > 0 ? gemm_block128_kernel<true, true>
+                        : (bf16 ? gemm_block128_kernel<true, false> : gemm_block128_kernel<false, false>);
+  static bool done[3][64] = {};
+  rc = ensure_smem_limit(kern, kSmemBytes, done[inter > 0 ? 2 : (bf16 ? 1 : 0)]);
   if (rc != BFP8_OK) return rc;
   kern<<<grid, kThreads, kSmemBytes, st>>>(tmap_a, tmap_w, tmap_out, p);
   BFP8_CUDA_TRY(cudaGetLastError());

@@ -172,6 +172,30 @@ int bfp8_gemm_block128_noalloc(const uint8_t* a_codes, int64_t lda, const float*
                                int64_t m, int64_t n, int64_t k,
                                uint32_t* status_dev, void* stream);
 
+/* Load-time repack for bfp8_gemm_block128_swiglu: w_codes is the fused gate/up weight [2 * inter, k] (rows
+ * [0, inter) gate, rows [inter, 2 * inter) up - the column order csrc/tpc/generic_dense/silu_and_mul_bf16.c:29
+ * reads, `col` and `col + width`); out receives the same rows interleaved in chunks of 64: chunk c holds gate
+ * rows 64c..64c+63 followed by up rows 64c..64c+63.  Codes are copied unchanged, the scale grid is not
+ * touched.  inter must be a multiple of 128 (BFP8_ERR_UNSUPPORTED otherwise), k and both leading
+ * dimensions multiples of 16; not in place. */
+int bfp8_swiglu_interleave_weight(const uint8_t* w_codes, int64_t ld_src, uint8_t* out, int64_t ld_dst,
+                                  int64_t inter, int64_t k, void* stream);
+
+/* Gate/up GEMM with the SwiGLU step fused into its epilogue:
+ *   gate = bf16(A . Wgate^T (+ bias[0:inter])),  up = bf16(A . Wup^T (+ bias[inter:2 inter])),
+ *   out[i, j] = bf16( silu(gate[i, j]) * up[i, j] )                                    out: bf16 [m, inter]
+ * Replaces "block-scaled GEMM to bf16 [m, 2 * inter], then gk_silu_and_mul_bf16_v1"
+ * (csrc/tpc/generic_dense/silu_and_mul_bf16.c:4-13,16-75; glue csrc/host/generic_dense_glue.cpp:196-216):
+ * both factors are rounded to bf16 exactly where the unfused pair rounds them, silu(g) = g / (1 + exp(-g))
+ * with 0 for g <= -88, and the product is rounded once.  w_codes is the output of
+ * bfp8_swiglu_interleave_weight; w_scales ([2 * inter / 128, ceil(k/128)]) and bias ([2 * inter] or NULL)
+ * keep the fused weight's original order (gate first).  Other requirements as bfp8_gemm_block128;
+ * inter % 128 == 0.  Runs the large-tile schedule for every m; no workspace. */
+int bfp8_gemm_block128_swiglu(const uint8_t* a_codes, int64_t lda, const float* a_scales, int64_t ldsa,
+                              const uint8_t* w_codes, int64_t ldw, const float* w_scales,
+                              const float* bias, void* out, int64_t ldo,
+                              int64_t m, int64_t inter, int64_t k, uint32_t* status_dev, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

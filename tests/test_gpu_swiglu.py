@@ -1,0 +1,119 @@
+"""GPU parity of the gate/up GEMM with the fused SwiGLU epilogue (through the C ABI).
+
+The fused kernel is checked against the unfused pair it replaces - the library's own bf16 GEMM over the fused
+gate/up weight, which the other GPU tests pin to the oracle, followed by the CPU restatement of
+gk_silu_and_mul_bf16_v1 - and end to end against the oracle's bf16 GEMM result followed by the same restatement.
+"""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import block_fp8_ref, swiglu_ref
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def gk():
+    import gaudi_kernels_b200 as g
+    from gaudi_kernels_b200 import _lib
+    _lib.load()
+    return g
+
+
+def _problem(m, k, inter, seed, bias):
+    g = torch.Generator().manual_seed(seed)
+    x = (torch.randn((m, k), generator=g) * 1.5).to(torch.bfloat16)
+    w = torch.randn((2 * inter, k), generator=g) * 0.05
+    grid = (2 * inter // 128, (k + 127) // 128)
+    s = torch.rand(grid, generator=g) * 2e-3 + 5e-4
+    # quantize the fp32 weight block by block into OCP codes the way a checkpoint holds them
+    kp = grid[1] * 128
+    wp = torch.nn.functional.pad(w, (0, kp - k))
+    q = (wp.view(grid[0], 128, grid[1], 128) / s.view(grid[0], 1, grid[1], 1)).clamp(-448, 448)
+    codes = q.view(2 * inter, kp)[:, :k].contiguous().to(torch.float8_e4m3fn)
+    b = (torch.randn(2 * inter, generator=g) * 0.3) if bias else None
+    return x, codes, s, b
+
+
+def _bf16_step(t):
+    """Spacing of bf16 numbers at |t| (t is bf16)."""
+    a = t.float().abs().clamp_min(2.0 ** -126)
+    return torch.exp2(torch.floor(torch.log2(a)) - 7).double()
+
+
+@pytest.mark.parametrize("inter,k", [(128, 128), (256, 1040), (1024, 512)])
+def test_interleave_is_the_documented_row_order(gk, inter, k):
+    rng = np.random.default_rng(inter + k)
+    w = rng.integers(0, 256, size=(2 * inter, k), dtype=np.uint8)
+    w[w == 0x7f] = 0x7e
+    w[w == 0xff] = 0xfe
+    s = np.ones((2 * inter // 128, (k + 127) // 128), dtype=np.float32)
+    got, s_out = gk.prepare_weight_swiglu(torch.from_numpy(w).cuda(), torch.from_numpy(s).cuda(), native_half=False)
+    assert torch.equal(s_out.cpu(), torch.from_numpy(s))
+    assert np.array_equal(got.view(torch.uint8).cpu().numpy()[:, :k], swiglu_ref.interleave_gate_up(w))
+
+
+@pytest.mark.parametrize("m,k,inter,bias", [(1, 128, 128, False), (37, 384, 256, True), (130, 208, 384, False),
+                                            (256, 1024, 1024, True), (300, 1000, 512, True), (2048, 512, 2048, False)])
+@pytest.mark.parametrize("half", [True, False])
+def test_fused_swiglu_matches_gemm_then_silu_and_mul(gk, m, k, inter, bias, half):
+    x, codes, s, b = _problem(m, k, inter, seed=m * 7 + inter + k, bias=bias)
+    xd = x.cuda()
+    a_codes, a_scales = gk.quantize_act_1x128(xd, native_half=half)
+    # the unfused pair: bf16 GEMM over the fused weight, then the restated silu_and_mul
+    w_plain, s_plain = gk.prepare_weight(codes.cuda(), s.cuda(), native_half=half)
+    bd = None if b is None else b.cuda()
+    gate_up = gk.gemm_block_fp8(a_codes, a_scales, w_plain, s_plain, bias=bd, schedule=1).cpu()
+    want = swiglu_ref.silu_and_mul_bf16(gate_up)
+    w_il, s_il = gk.prepare_weight_swiglu(codes.cuda(), s.cuda(), native_half=half)
+    got = gk.gemm_block_fp8_swiglu(a_codes, a_scales, w_il, s_il, bias=bd).cpu()
+    assert got.dtype == torch.bfloat16 and tuple(got.shape) == (m, inter)
+    # same accumulation and the same bf16 rounding of both factors: only the last bit of the product may differ
+    diff = (got.double() - want.double()).abs()
+    assert bool((diff <= _bf16_step(want) + 1e-36).all()), float((diff - _bf16_step(want)).max())
+    assert float((got != want).float().mean()) < 0.02
+    # end to end against the oracle's GEMM followed by the same step: the GEMM's tolerance (1e-2 of the RMS
+    # before rounding, here on each factor) plus the bf16 steps the two roundings can move a product by
+    y64, ybf = block_fp8_ref.reference_rows(x, codes, s, native_half=half, bias=b)
+    want2 = swiglu_ref.silu_and_mul_bf16(ybf)
+    rms = float(want2.double().pow(2).mean().sqrt())
+    diff2 = (got.double() - want2.double()).abs()
+    assert bool((diff2 <= 3e-2 * rms + 3.0 * _bf16_step(want2)).all()), float(diff2.max())
+
+
+def test_silu_special_values(gk):
+    """g <= -88 gives exactly 0; large positive g passes through; rows beyond M are not written."""
+    m, k, inter = 5, 128, 128
+    x = torch.zeros((m, k), dtype=torch.bfloat16)
+    x[:, 0] = torch.tensor([1.0, -1.0, 0.5, -0.5, 0.0]).to(torch.bfloat16)
+    w = torch.zeros((2 * inter, k))
+    w[:inter, 0] = torch.linspace(-448, 448, inter)
+    w[inter:, 0] = 1.0
+    codes = w.to(torch.float8_e4m3fn)
+    s = torch.full((2, 1), 0.5)
+    a_codes, a_scales = gk.quantize_act_1x128(x.cuda(), native_half=True)
+    w_il, s_il = gk.prepare_weight_swiglu(codes.cuda(), s.cuda(), native_half=True)
+    canvas = torch.full((m + 3, inter), 7.0, dtype=torch.bfloat16, device="cuda")
+    got = gk.gemm_block_fp8_swiglu(a_codes, a_scales, w_il, s_il, out=canvas[:m]).cpu()
+    assert bool((canvas[m:] == 7.0).all())
+    y64, ybf = block_fp8_ref.reference_rows(x, codes, s, native_half=True)
+    want = swiglu_ref.silu_and_mul_bf16(ybf)
+    assert float(ybf[:, :inter].min()) <= -88.0 and float(ybf[:, :inter].max()) >= 88.0
+    diff = (got.double() - want.double()).abs()
+    assert bool((diff <= _bf16_step(want) + 1e-36).all())
+    assert bool((got[ybf[:, :inter] <= -88.0] == 0).all())
+
+
+def test_swiglu_rejects_bad_arguments(gk):
+    x = torch.zeros((4, 128), dtype=torch.bfloat16, device="cuda")
+    a_codes, a_scales = gk.quantize_act_1x128(x, native_half=True)
+    w = torch.zeros((192, 128), dtype=torch.uint8, device="cuda")          # I = 96: not a multiple of 128
+    with pytest.raises(ValueError):
+        gk.prepare_weight_swiglu(w.view(torch.float8_e4m3fn), torch.ones((2, 1), device="cuda"))
+    w = torch.zeros((256, 128), dtype=torch.uint8, device="cuda")
+    with pytest.raises(ValueError):
+        gk.gemm_block_fp8_swiglu(a_codes, a_scales, w, torch.ones((3, 1), device="cuda"))
+    with pytest.raises(ValueError):
+        gk.gemm_block_fp8_swiglu(a_codes, a_scales, w, torch.ones((2, 1), device="cuda"), bias=torch.zeros(100))
