@@ -11,6 +11,12 @@
 //     last CTA to arrive at a tile (per-tile counter) adds the partials in CTA order - a fixed order,
 //     so results do not depend on timing - applies the bias and stores the tile.  Counters are
 //     returned to zero, so a zero-initialised workspace stays reusable.
+// When there are at most half as many tiles as SMs, the CTAs that share a tile form a thread-block cluster
+// (2, 4 or 8 CTAs, each with an equal slice of the K range) and exchange their partials through distributed
+// shared memory instead: every CTA owns MP / cluster-size of the padded activation rows, receives those rows
+// from all CTAs of the cluster into the (by then idle) pipeline buffers, adds them in rank order - again a
+// fixed order - and stores its rows.  Two cluster barriers replace the store / fence / counter / read-back
+// round trip through global memory.
 // Each K block is accumulated from zero into one of four small TMEM buffers and folded into register
 // accumulators with its scale product sa[g, i] * sw[j/128, g], as in the large-tile schedule.
 //
@@ -73,6 +79,7 @@ struct Params {
   long long total_units;
   long long wait_limit;
   uint32_t* status;
+  int cluster;             // CTAs per tile when the kernel runs as clusters (kCluster), else unused
 };
 
 // First unit of CTA c when `total` units are split over `parts` CTAs.
@@ -84,7 +91,7 @@ __host__ __device__ inline int cta_of_unit(long long u, long long total, long lo
   return static_cast<int>(((u + 1) * parts - 1) / total);
 }
 
-template <int MP>
+template <int MP, bool kCluster>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a,
                    const Params p) {
@@ -99,8 +106,14 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   const int lane = threadIdx.x & 31;
   const int G = p.groups;
   const long long parts = gridDim.x;
-  const long long u0 = first_unit(blockIdx.x, p.total_units, parts);
-  const long long u1 = first_unit(blockIdx.x + 1, p.total_units, parts);
+  // kCluster: cluster c works on tile c and CTA r of it on K blocks [r G / cs, (r + 1) G / cs)
+  const int cs = kCluster ? p.cluster : 1;
+  const int crank = kCluster ? static_cast<int>(blockIdx.x % cs) : 0;
+  const long long ctile = blockIdx.x / cs;
+  const long long u0 = kCluster ? ctile * G + static_cast<long long>(crank) * G / cs
+                                : first_unit(blockIdx.x, p.total_units, parts);
+  const long long u1 = kCluster ? ctile * G + static_cast<long long>(crank + 1) * G / cs
+                                : first_unit(blockIdx.x + 1, p.total_units, parts);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::kStages; ++s) {
@@ -255,7 +268,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&tail->tmem_empty[buf]));
 
-      if (g == G - 1 || u == u1 - 1) {
+      if (!kCluster && (g == G - 1 || u == u1 - 1)) {
         // ---- end of this CTA's segment of the tile
         const long long tile_first = static_cast<long long>(tile) * G;
         const int c_first = cta_of_unit(tile_first, p.total_units, parts);
@@ -312,6 +325,46 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         seg_start = u + 1;
       }
     }
+    if (kCluster) {
+      // ---- reduce-scatter of the cluster's partials through distributed shared memory
+      // #1: every CTA of the cluster is done with its pipeline buffers, which now receive the partials
+      ptx::cluster_sync_all();
+      const int rows_per = MP / cs;                               // padded rows each CTA owns (cs divides MP)
+      const int shift = 31 - __clz(rows_per);
+      const uint32_t recv = smem_base;                            // [source rank][row of the owner][weight row] fp32
+      if (ok) {
+#pragma unroll
+        for (int j = 0; j < MP; ++j) {
+          if (j < p.m) {
+            const uint32_t owner = static_cast<uint32_t>(j >> shift), jj = static_cast<uint32_t>(j & (rows_per - 1));
+            ptx::st_cluster_f32(ptx::cluster_map(recv, owner) + ((crank * rows_per + jj) * BN + wrow) * 4u, acc[j]);
+          }
+        }
+      }
+      // #2: all partials have arrived
+      ptx::cluster_sync_all();
+      const int col = static_cast<int>(ctile) * BN + wrow;
+      if (ok && col < p.n) {
+        const float b = p.bias != nullptr ? __ldg(p.bias + col) : 0.0f;
+        const float* mine = reinterpret_cast<const float*>(smem);
+        for (int jj = 0; jj < rows_per; ++jj) {
+          const int j = crank * rows_per + jj;
+          if (j >= p.m) break;
+          float sum = 0.0f;
+          for (int r = 0; r < cs; ++r) sum += mine[(r * rows_per + jj) * BN + wrow];   // rank order = K order
+          sum += b;
+          if (p.out_bf16)
+            reinterpret_cast<uint16_t*>(p.out)[static_cast<int64_t>(j) * p.ldo + col] = static_cast<uint16_t>(float_to_bf16_bits(sum));
+          else
+            reinterpret_cast<float*>(p.out)[static_cast<int64_t>(j) * p.ldo + col] = sum;
+        }
+      }
+    }
+  }
+  if (kCluster && warp >= kEpiWarps) {
+    // the other roles take part in the two cluster barriers of the exchange
+    ptx::cluster_sync_all();
+    ptx::cluster_sync_all();
   }
 
   // ------------------------------------------------------------------ teardown
@@ -327,10 +380,48 @@ int launch(const CUtensorMap& tmap_w, const CUtensorMap& tmap_a, const Params& p
   using C = Cfg<MP>;
   constexpr int smem = 1024 + C::kStages * C::kStageBytes + sizeof(SmemTail);
   static bool done[64] = {};
-  const int rc = ensure_smem_limit(gemm_smallm_kernel<MP>, smem, done);
+  const int rc = ensure_smem_limit(gemm_smallm_kernel<MP, false>, smem, done);
   if (rc != BFP8_OK) return rc;
-  gemm_smallm_kernel<MP><<<grid, kThreads, smem, st>>>(tmap_w, tmap_a, p);
+  gemm_smallm_kernel<MP, false><<<grid, kThreads, smem, st>>>(tmap_w, tmap_a, p);
   BFP8_CUDA_TRY(cudaGetLastError());
+  return BFP8_OK;
+}
+
+// Cluster form: p.tiles clusters of p.cluster CTAs.  Returns BFP8_ERR_UNSUPPORTED without launching when the
+// device cannot hold all clusters at once (the caller then uses the plain form).
+template <int MP>
+int launch_clustered(const CUtensorMap& tmap_w, const CUtensorMap& tmap_a, const Params& p, cudaStream_t st) {
+  using C = Cfg<MP>;
+  constexpr int smem = 1024 + C::kStages * C::kStageBytes + sizeof(SmemTail);
+  static_assert(MP * BN * 4 <= C::kStages * C::kStageBytes, "the exchange area reuses the pipeline buffers");
+  static bool done[64] = {};
+  const int rc = ensure_smem_limit(gemm_smallm_kernel<MP, true>, smem, done);
+  if (rc != BFP8_OK) return rc;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(p.tiles * p.cluster), 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = static_cast<unsigned>(p.cluster);
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  // co-residency of all clusters, asked once per device and cluster size (index log2(cluster) - 1)
+  static int max_clusters[64][3] = {};
+  int dev = 0;
+  BFP8_CUDA_TRY(cudaGetDevice(&dev));
+  const int slot = p.cluster == 2 ? 0 : p.cluster == 4 ? 1 : 2;
+  int cap = (dev >= 0 && dev < 64) ? max_clusters[dev][slot] : 0;
+  if (cap == 0) {
+    BFP8_CUDA_TRY(cudaOccupancyMaxActiveClusters(&cap, gemm_smallm_kernel<MP, true>, &cfg));
+    if (cap <= 0) cap = -1;
+    if (dev >= 0 && dev < 64) max_clusters[dev][slot] = cap;
+  }
+  if (cap < p.tiles) return BFP8_ERR_UNSUPPORTED;
+  BFP8_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_smallm_kernel<MP, true>, tmap_w, tmap_a, p));
   return BFP8_OK;
 }
 
@@ -368,10 +459,22 @@ int smallm_grid(int64_t tiles, int64_t groups, int sms) {
   return sms;
 }
 
+// CTAs per tile for the cluster form, or 0 when it does not apply: at most half as many tiles as SMs, a
+// power of two up to the portable cluster size of 8, and no more CTAs than the tile has K blocks.
+int smallm_cluster_size(int64_t tiles, int64_t groups, int sms) {
+  if (tiles * 2 > sms) return 0;
+  const long long per_tile = sms / tiles;
+  int cs = per_tile >= 8 ? 8 : per_tile >= 4 ? 4 : 2;
+  while (cs > groups) cs >>= 1;
+  return cs >= 2 ? cs : 0;
+}
+
 int launch_gemm_smallm(const uint8_t* a_codes, int64_t lda, const float* a_scales, int64_t ldsa,
                        const uint8_t* w_codes, int64_t ldw, const float* w_scales, const float* bias, void* out,
                        int out_dtype, int64_t ldo, int64_t m, int64_t n, int64_t k, void* workspace,
                        uint32_t* status_dev, long long wait_limit, int max_ctas, cudaStream_t st) {
+  // max_ctas > 0 (a caller-imposed CTA limit, used by tests and by the entry point with the built-in scratch)
+  // also keeps the launch on the plain, non-cluster form
   const int mp = smallm_padded_rows(m);
   alignas(64) CUtensorMap tmap_w, tmap_a;
   int rc = make_tensor_map_2d(&tmap_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, w_codes, k, n, ldw, BK, BN);
@@ -398,6 +501,18 @@ int launch_gemm_smallm(const uint8_t* a_codes, int64_t lda, const float* a_scale
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   p.counters = reinterpret_cast<uint32_t*>(workspace);
   p.partials = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + kCounterBytes);
+  p.cluster = max_ctas > 0 ? 0 : smallm_cluster_size(p.tiles, p.groups, sms);
+  if (p.cluster >= 2) {
+    int crc;
+    switch (mp) {
+      case 16: crc = launch_clustered<16>(tmap_w, tmap_a, p, st); break;
+      case 32: crc = launch_clustered<32>(tmap_w, tmap_a, p, st); break;
+      case 64: crc = launch_clustered<64>(tmap_w, tmap_a, p, st); break;
+      default: crc = launch_clustered<128>(tmap_w, tmap_a, p, st); break;
+    }
+    if (crc != BFP8_ERR_UNSUPPORTED) return crc;
+    p.cluster = 0;
+  }
   switch (mp) {
     case 16: return launch<16>(tmap_w, tmap_a, p, grid, st);
     case 32: return launch<32>(tmap_w, tmap_a, p, grid, st);

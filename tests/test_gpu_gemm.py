@@ -163,6 +163,27 @@ def test_gemm_small_m_ragged(gk, m, k, n):
         assert bool((buf[m:] == 0.25).all()) and bool((buf[:, n:] == 0.25).all())
 
 
+@pytest.mark.parametrize("m,k,n", [(1, 14336, 4096), (64, 14336, 4096), (16, 2048, 2048), (128, 1024, 1024), (5, 384, 9000)])
+def test_gemm_small_m_cluster_exchange(gk, m, k, n):
+    # few tiles: the CTAs of a tile form a cluster and add their K slices through distributed shared memory
+    # (2, 4 or 8 CTAs per tile for these shapes); a caller-imposed CTA limit selects the global-memory form
+    x, w, s, b = _random_problem(m, k, n, seed=m * 3 + n, bias=(m > 1))
+    y64, ybf = block_fp8_ref.reference_rows(x, w, s, native_half=True, bias=b)
+    rms = float(y64.pow(2).mean().sqrt())
+    a_codes, a_scales = gk.quantize_act_1x128(x.cuda(), native_half=True)
+    wc, ws = gk.prepare_weight(w, s, native_half=True)
+    bd = None if b is None else b.cuda()
+    out = gk.gemm_block_fp8(a_codes, a_scales, wc, ws, bias=bd, out_dtype=torch.float32, schedule=2)
+    assert float((out.double().cpu() - y64).abs().max()) / rms <= TOL
+    again = gk.gemm_block_fp8(a_codes, a_scales, wc, ws, bias=bd, out_dtype=torch.float32, schedule=2)
+    assert torch.equal(out, again)                                         # fixed summation order
+    plain = gk.gemm_block_fp8(a_codes, a_scales, wc, ws, bias=bd, out_dtype=torch.float32, schedule=2, max_ctas=148)
+    assert float((plain.double().cpu() - y64).abs().max()) / rms <= TOL
+    assert float((plain - out).abs().max()) <= 1e-5 * rms + 1e-30       # same K slices up to fp32 association
+    out16 = gk.gemm_block_fp8(a_codes, a_scales, wc, ws, bias=bd)
+    assert torch.equal(out16, out.to(torch.bfloat16))
+
+
 def test_gemm_output_tail_is_untouched(gk):
     # sentinel columns right of N and rows below M must survive (out-of-bounds write check)
     m, k, n = 70, 256, 203
