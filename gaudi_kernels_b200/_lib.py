@@ -36,6 +36,14 @@ SIGNATURES = {
                                        _i64, _i64, _i64, _ptr, _ptr]),
     "bfp8_gemm_block128_noalloc": (_int, [_ptr, _i64, _ptr, _i64, _ptr, _i64, _ptr, _ptr, _ptr, _int, _i64,
                                           _i64, _i64, _i64, _ptr, _ptr]),
+    "bfp8_rank_sum": (_int, [_ptr, _ptr, _i64, _int, _int, _ptr]),
+    "bfp8_rank_sum_slices": (_int, [_ptr, _ptr, _i64, _int, _int, _ptr, _i64, _ptr]),
+    "bfp8_peer_alloc": (_int, [_sz, _ptr]),
+    "bfp8_peer_free": (_int, [_ptr]),
+    "bfp8_peer_export": (_int, [_ptr, _ptr]),
+    "bfp8_peer_open": (_int, [_ptr, _ptr]),
+    "bfp8_peer_close": (_int, [_ptr]),
+    "bfp8_peer_barrier": (_int, [_ptr, _int, _int, _c.c_uint32, _i64, _ptr, _ptr]),
     "bfp8_swiglu_interleave_weight": (_int, [_ptr, _i64, _ptr, _i64, _i64, _i64, _ptr]),
     "bfp8_gemm_block128_swiglu": (_int, [_ptr, _i64, _ptr, _i64, _ptr, _i64, _ptr, _ptr, _ptr, _i64,
                                          _i64, _i64, _i64, _ptr, _ptr]),

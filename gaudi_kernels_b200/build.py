@@ -16,7 +16,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 LIB = os.path.join(HERE, "libbfp8.so")
-SOURCES = ["codec.cu", "gemm_tcgen05.cu", "gemm_smallm.cu", "gemm_pair.cu", "gemm_channel.cu", "gemm_api.cu"]
+SOURCES = ["codec.cu", "gemm_tcgen05.cu", "gemm_smallm.cu", "gemm_pair.cu", "gemm_channel.cu", "gemm_api.cu",
+           "rank_sum.cu"]
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 CFLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-I" + INCLUDE, "-I" + CSRC]
 

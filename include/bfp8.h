@@ -33,7 +33,7 @@ extern "C" {
 #define BFP8_ERR_SHAPE       -3   /* a size is zero, negative or outside the supported range */
 #define BFP8_ERR_WORKSPACE   -4   /* workspace smaller than bfp8_*_workspace_bytes() */
 #define BFP8_ERR_CUDA        -5   /* a CUDA runtime / driver call failed (see bfp8_last_cuda_error) */
-#define BFP8_ERR_UNSUPPORTED -6   /* the device is not an sm_100 part */
+#define BFP8_ERR_UNSUPPORTED -6   /* not an sm_100 part, or a configuration the entry point states it does not take */
 #define BFP8_ERR_TOO_LARGE   -7   /* the problem exceeds the fixed scratch of bfp8_gemm_block128_noalloc */
 
 #define BFP8_STATUS_NONFINITE_CODE 0x1u  /* an input byte was 0x7f or 0xff (OCP E4M3FN NaN) */
@@ -195,6 +195,42 @@ int bfp8_gemm_block128_swiglu(const uint8_t* a_codes, int64_t lda, const float* 
                               const uint8_t* w_codes, int64_t ldw, const float* w_scales,
                               const float* bias, void* out, int64_t ldo,
                               int64_t m, int64_t inter, int64_t k, uint32_t* status_dev, void* stream);
+
+/* Sum of world_size per-rank slices in canonical rank order: dst[i] = ((s0[i] + s1[i]) + s2[i]) + ... in fp32,
+ * rounded once (RNE) for bf16 data.  Replaces gk_rank_sum_bf16_v1 / gk_rank_sum_f32_v1
+ * (csrc/tpc/generic_dense/rank_sum.c:4-42; glue csrc/host/generic_dense_glue.cpp:569-600): `gathered` holds the
+ * slices back to back ([world_size * elems]), dst is [elems], both of `dtype` (BFP8_OUT_F32 / BFP8_OUT_BF16);
+ * world_size 2..8 as there (BFP8_ERR_UNSUPPORTED otherwise). */
+int bfp8_rank_sum(const void* gathered, void* dst, int64_t elems, int world_size, int dtype, void* stream);
+
+/* The same sum over slices given by pointer (`slices` is a HOST array of world_size device pointers), which is
+ * what the K-sharded GEMM uses: slice r may be memory of GPU r opened with bfp8_peer_open, so no gather precedes
+ * the sum - the kernel reads every slice once through plain peer loads.  Optional bias: fp32, added after the
+ * sum as bias[i % bias_period] (the slices then start at column 0 of a row of bias_period values). */
+int bfp8_rank_sum_slices(const void* const* slices, void* dst, int64_t elems, int world_size, int dtype,
+                         const float* bias, int64_t bias_period, void* stream);
+
+/* Device memory that other processes on the same machine can map (one process per GPU).  These have no
+ * counterpart in the reference, whose cross-device exchange lives in the external runtime
+ * (csrc/tpc/generic_dense/rank_sum.c:2 only sees gathered data).
+ *   bfp8_peer_alloc   cudaMalloc + zero fill on the current device (synchronous; set-up time only)
+ *   bfp8_peer_export  64-byte handle of such an allocation, to be sent to the other ranks by any host channel
+ *   bfp8_peer_open    map another rank's allocation into this process; the pointer is valid on the current device
+ *   bfp8_peer_close / bfp8_peer_free   undo open / alloc */
+int bfp8_peer_alloc(size_t bytes, void** ptr);
+int bfp8_peer_free(void* ptr);
+int bfp8_peer_export(void* ptr, uint8_t handle[64]);
+int bfp8_peer_open(const uint8_t handle[64], void** ptr);
+int bfp8_peer_close(void* ptr);
+
+/* Stream-ordered barrier between the ranks' GPUs.  `flags` is a HOST array of world_size device pointers:
+ * flags[r] is rank r's flag array (world_size uint32, zero at start, in bfp8_peer_alloc memory; flags[rank] is
+ * this rank's own).  The kernel publishes `epoch` (use 1, 2, 3, ... on every rank alike) to every rank and waits
+ * until every rank has published it; work enqueued on `stream` before the call is visible to the other ranks'
+ * GPUs once their barrier returns.  The wait is bounded (wait_limit_cycles, 0 = about two seconds): on expiry
+ * BFP8_STATUS_WAIT_TIMEOUT is raised in *status_dev and the kernel returns.  Each rank must run on its own GPU. */
+int bfp8_peer_barrier(uint32_t* const* flags, int rank, int world_size, uint32_t epoch,
+                      int64_t wait_limit_cycles, uint32_t* status_dev, void* stream);
 
 #ifdef __cplusplus
 }

@@ -88,3 +88,37 @@ def test_no_silent_fallback_without_a_gpu():
     w = torch.zeros(16, dtype=torch.uint8).view(torch.float8_e4m3fn)
     with pytest.raises(Bfp8Error):
         gk.reencode_e4m3fn_half(w, torch.ones(1))
+
+
+def test_rank_sum_contract_without_gpu():
+    """World sizes outside 2..8 are refused before any CUDA call (generic_dense_glue.cpp:576), as are null
+    pointers and empty slices; the CPU restatement applies the same rule."""
+    import ctypes
+    from gaudi_kernels_b200 import _lib
+    from oracle import rank_sum_ref
+    lib = _lib.load()
+    buf = (ctypes.c_float * 64)()
+    for world in (1, 9, 0, -3):
+        assert lib.bfp8_rank_sum(buf, buf, 8, world, _lib.OUT_F32, None) == -6          # BFP8_ERR_UNSUPPORTED
+        with pytest.raises(ValueError):
+            rank_sum_ref.check_contract(8 * max(world, 1), 8, world)
+    assert lib.bfp8_rank_sum(None, buf, 8, 4, _lib.OUT_F32, None) == -1
+    assert lib.bfp8_rank_sum(buf, buf, 0, 4, _lib.OUT_F32, None) == -3          # BFP8_ERR_SHAPE
+    assert lib.bfp8_rank_sum(buf, buf, 8, 4, 7, None) == -3
+    with pytest.raises(ValueError):
+        rank_sum_ref.check_contract(8192, 4096, 4)                # mismatched gathered size (contract test :584)
+    rank_sum_ref.check_contract(16384, 4096, 4)
+
+
+def test_rank_sum_restatement_known_answers():
+    import torch
+    from oracle import rank_sum_ref
+    # fp32: (1e8 + 1) - 1e8 = 0 in rank order 0,1,2 but 1 in the order 0,2,1
+    x = torch.tensor([1e8, 1.0, -1e8], dtype=torch.float32)
+    assert float(rank_sum_ref.rank_sum(x, 3)[0]) == 0.0
+    # bf16: the sum is formed in fp32 and rounded once: 1 + 2^-8 + 2^-8 = 1 + 2^-7 is representable,
+    # whereas rounding after each addition would have stayed at 1
+    y = torch.tensor([1.0, 2.0 ** -8, 2.0 ** -8], dtype=torch.bfloat16)
+    assert float(rank_sum_ref.rank_sum(y, 3)[0]) == 1.0 + 2.0 ** -7
+    two = torch.tensor([1.5, -0.25, 2.0, 4.0], dtype=torch.float32)
+    assert rank_sum_ref.rank_sum(two, 2).tolist() == [3.5, 3.75]

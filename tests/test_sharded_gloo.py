@@ -62,3 +62,27 @@ def test_shard_bounds():
         sharded.shard_bounds(14336, 3, 0)                     # 112 block rows do not split over 3 ranks
     with pytest.raises(ValueError):
         sharded.shard_bounds(1024, 2, 2)
+
+
+def test_row_parallel_bounds_cover_everything_once():
+    """K slices are whole scale blocks, row slices are contiguous; both partition their range for every world size."""
+    from gaudi_kernels_b200.row_parallel import k_shard_bounds, row_bounds
+    import pytest
+    for world in range(1, 9):
+        for k in (1024, 1152, 4096, 14336, 1000, 28672):
+            if (k + 127) // 128 < world:
+                with pytest.raises(ValueError):
+                    k_shard_bounds(k, world, 0)
+                continue
+            edges = [k_shard_bounds(k, world, r) for r in range(world)]
+            assert edges[0][0] == 0 and edges[-1][1] == k
+            for (a0, a1), (b0, b1) in zip(edges, edges[1:]):
+                assert a1 == b0 and a0 % 128 == 0 and a1 % 128 == 0 and a1 > a0
+            sizes = [(b - a + 127) // 128 for a, b in edges]
+            assert max(sizes) - min(sizes) <= 1
+        for m in (1, 5, 8, 300, 8192):
+            rows = [row_bounds(m, world, r) for r in range(world)]
+            assert rows[0][0] == 0 and rows[-1][1] == m
+            assert all(a[1] == b[0] for a, b in zip(rows, rows[1:]))
+    with pytest.raises(ValueError):
+        k_shard_bounds(1024, 4, 4)
