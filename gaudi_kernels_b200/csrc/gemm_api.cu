@@ -2,10 +2,15 @@
 #include "common.cuh"
 
 namespace bfp8 {
+struct PushTarget {
+  const void* recv[8];
+  int world, rank, rows;
+};
 int launch_gemm_large(const uint8_t* a_codes, int64_t lda, const float* a_scales, int64_t ldsa,
                       const uint8_t* w_codes, int64_t ldw, const float* w_scales, const float* bias, void* out,
                       int out_dtype, int64_t ldo, int64_t m, int64_t n, int64_t k, uint32_t* status_dev,
-                      long long wait_limit, int max_ctas, int band, int inter, cudaStream_t st);
+                      long long wait_limit, int max_ctas, int band, int inter, const PushTarget* push,
+                      cudaStream_t st);
 int launch_gemm_pair(const uint8_t* a_codes, int64_t lda, const float* a_scales, int64_t ldsa,
                      const uint8_t* w_codes, int64_t ldw, const float* w_scales, const float* bias, void* out,
                      int out_dtype, int64_t ldo, int64_t m, int64_t n, int64_t k, uint32_t* status_dev,
@@ -70,7 +75,7 @@ extern "C" int bfp8_gemm_block128_ex(const uint8_t* a_codes, int64_t lda, const 
     return launch_gemm_pair(a_codes, lda, a_scales, ldsa, w_codes, ldw, w_scales, bias, out, out_dtype, ldo, m, n, k,
                             status_dev, limit, max_ctas, st);
   return launch_gemm_large(a_codes, lda, a_scales, ldsa, w_codes, ldw, w_scales, bias, out, out_dtype, ldo, m, n, k,
-                           status_dev, limit, max_ctas, /*band=*/0, /*inter=*/0, st);
+                           status_dev, limit, max_ctas, /*band=*/0, /*inter=*/0, /*push=*/nullptr, st);
 }
 
 extern "C" int bfp8_gemm_block128(const uint8_t* a_codes, int64_t lda, const float* a_scales, int64_t ldsa,
@@ -152,5 +157,32 @@ extern "C" int bfp8_gemm_block128_swiglu(const uint8_t* a_codes, int64_t lda, co
   if (!aligned(out, 16) || ldo % 8 != 0) return BFP8_ERR_ALIGN;
   return launch_gemm_large(a_codes, lda, a_scales, ldsa, w_codes, ldw, w_scales, bias, out, BFP8_OUT_BF16, ldo,
                            m, 2 * inter, k, status_dev, kDefaultWaitLimit, 0, /*band=*/0, static_cast<int>(inter),
+                           /*push=*/nullptr, static_cast<cudaStream_t>(stream));
+}
+
+// ---- row-parallel GEMM whose epilogue scatters its tiles to the GPUs that reduce them -------------------
+
+extern "C" int bfp8_gemm_block128_push(const uint8_t* a_codes, int64_t lda, const float* a_scales, int64_t ldsa,
+                                       const uint8_t* w_codes, int64_t ldw, const float* w_scales,
+                                       void* const* recv, int rank, int world_size,
+                                       int64_t m, int64_t n, int64_t k, uint32_t* status_dev, void* stream) {
+  if (!a_codes || !a_scales || !w_codes || !w_scales || !recv || !status_dev) return BFP8_ERR_NULL;
+  if (m <= 0 || n <= 0 || k <= 0 || m > (1 << 30) || n > (1 << 30) || k > (1 << 30)) return BFP8_ERR_SHAPE;
+  if (world_size < 2 || world_size > 8 || rank < 0 || rank >= world_size) return BFP8_ERR_UNSUPPORTED;
+  if (lda < k || ldw < k || ldsa < m) return BFP8_ERR_SHAPE;
+  if (m % (128 * world_size) != 0 || n % 64 != 0) return BFP8_ERR_UNSUPPORTED;
+  if (!aligned(a_codes, 16) || !aligned(w_codes, 16) || lda % 16 != 0 || ldw % 16 != 0) return BFP8_ERR_ALIGN;
+  if (!aligned(a_scales, 4) || !aligned(w_scales, 4) || !aligned(status_dev, 4)) return BFP8_ERR_ALIGN;
+  PushTarget t = {};
+  for (int o = 0; o < world_size; ++o) {
+    if (!recv[o]) return BFP8_ERR_NULL;
+    if (!aligned(recv[o], 16)) return BFP8_ERR_ALIGN;
+    t.recv[o] = recv[o];
+  }
+  t.world = world_size;
+  t.rank = rank;
+  t.rows = static_cast<int>(m / world_size);
+  return launch_gemm_large(a_codes, lda, a_scales, ldsa, w_codes, ldw, w_scales, nullptr, const_cast<void*>(t.recv[rank]),
+                           BFP8_OUT_BF16, n, m, n, k, status_dev, kDefaultWaitLimit, 0, /*band=*/0, /*inter=*/0, &t,
                            static_cast<cudaStream_t>(stream));
 }

@@ -24,6 +24,7 @@
 // buffer ready) and the producer (shared-memory stage free).  The kernel is persistent: one CTA per SM walks a static tile
 // list.  Every barrier wait is bounded; on expiry the CTA raises BFP8_STATUS_WAIT_TIMEOUT and leaves.
 #include <cuda.h>
+#include <string.h>
 
 #include "common.cuh"
 #include "ptx.cuh"
@@ -55,6 +56,11 @@ struct SmemTail {
 
 constexpr int kSmemBytes = 1024 /* alignment slack */ + kStages * kStageBytes + kOutStageBytes + sizeof(SmemTail);
 
+// One output tensor map per destination GPU of the push mode.
+struct PushMaps {
+  CUtensorMap m[8];
+};
+
 struct GemmParams {
   const float* a_scales;   // [G, ldsa]
   const float* w_scales;   // [NB, G]
@@ -65,15 +71,26 @@ struct GemmParams {
   int tiles_m, tiles_n;
   int band;                // tile-rows per band of the tile walk
   int inter;               // SwiGLU only: width of the gate and of the up projection (N = 2 * inter)
+  // Push mode (row-parallel GEMM): the bf16 tile of rows [o R, (o + 1) R) goes to GPU o, into slot `push_rank` of
+  // its receive area [push_world][R][N]; push_world == 0 stores to `out` as usual
+  int push_world, push_rank, push_rows;
+  int band_shift;          // the tile walk starts at this band (all bands full), so that ranks push to different owners
   long long wait_limit;
   uint32_t* status;
 };
 
 // Tiles are walked in bands of 16 tile-rows: consecutive tile indices share W tiles inside a band,
 // so the CTAs running at any moment touch a compact set of A and W tiles in L2.
-__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int kBand, int& tm, int& tn) {
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int kBand, int shift, int& tm, int& tn) {
   const int per_band = kBand * tiles_n;
-  const int band = t / per_band;
+  int band = t / per_band;
+  const int r0 = t - band * per_band;
+  if (shift != 0) {                       // only used when kBand divides tiles_m
+    band += shift;
+    const int nbands = tiles_m / kBand;
+    band -= (band / nbands) * nbands;
+    t = band * per_band + r0;
+  }
   const int first = band * kBand;
   const int rows = min(kBand, tiles_m - first);
   const int r = t - band * per_band;
@@ -95,7 +112,8 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
 template <bool kOutBf16, bool kSwiGLU>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_block128_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
-                     const __grid_constant__ CUtensorMap tmap_out, const GemmParams p) {
+                     const __grid_constant__ CUtensorMap tmap_out, const __grid_constant__ PushMaps pmaps,
+                     const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
@@ -139,7 +157,7 @@ gemm_block128_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         int tm, tn;
-        tile_coords(t, p.tiles_m, p.tiles_n, p.band, tm, tn);
+        tile_coords(t, p.tiles_m, p.tiles_n, p.band, p.band_shift, tm, tn);
         for (int g = 0; g < G; ++g) {
           ok = ptx::mbar_wait(ptx::smem_u32(&tail->done[stage]), phase ^ 1u, abort_flag, p.wait_limit);
           if (!ok) break;
@@ -193,7 +211,7 @@ gemm_block128_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     }
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
       int tm, tn;
-      tile_coords(t, p.tiles_m, p.tiles_n, p.band, tm, tn);
+      tile_coords(t, p.tiles_m, p.tiles_n, p.band, p.band_shift, tm, tn);
       const int row = tm * BM + quad * 32 + lane;
       // first output column of this thread: 128 of the tile's 256, or with SwiGLU 64 of its 128 outputs
       const int col0 = kSwiGLU ? tn * 128 + wg * 64 : tn * BN + wg * 128;
@@ -355,7 +373,16 @@ gemm_block128_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           __syncwarp();
           if (lane == 0) {
             const int y = tm * BM + quad * 32;
-            if (y < p.m && col0 + b * 64 < p.n) ptx::tma_store_2d(&tmap_out, ptx::smem_u32(my_stage), col0 + b * 64, y);
+            if (y < p.m && col0 + b * 64 < p.n) {
+              if (p.push_world > 0) {
+                // a peer's memory is the destination: same bulk store, through that GPU's tensor map
+                const int owner = (tm * BM) / p.push_rows;
+                ptx::tma_store_2d(&pmaps.m[owner], ptx::smem_u32(my_stage), col0 + b * 64,
+                                  p.push_rank * p.push_rows + (y - owner * p.push_rows));
+              } else {
+                ptx::tma_store_2d(&tmap_out, ptx::smem_u32(my_stage), col0 + b * 64, y);
+              }
+            }
             ptx::tma_store_commit();
           }
         }
@@ -384,6 +411,12 @@ gemm_block128_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 }  // namespace
 
 // ---- host side ------------------------------------------------------------------------------------
+
+// Destination of the push mode: recv[o] is GPU o's receive area ([world][rows][n] bf16, mapped in this process).
+struct PushTarget {
+  const void* recv[8];
+  int world, rank, rows;
+};
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -423,15 +456,30 @@ int make_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* bas
 int launch_gemm_large(const uint8_t* a_codes, int64_t lda, const float* a_scales, int64_t ldsa,
                       const uint8_t* w_codes, int64_t ldw, const float* w_scales, const float* bias, void* out,
                       int out_dtype, int64_t ldo, int64_t m, int64_t n, int64_t k, uint32_t* status_dev,
-                      long long wait_limit, int max_ctas, int band, int inter, cudaStream_t st) {
+                      long long wait_limit, int max_ctas, int band, int inter, const PushTarget* push,
+                      cudaStream_t st) {
   // inter > 0 selects the SwiGLU epilogue: W has n = 2 * inter interleaved rows and the output is [m, inter] bf16
+  // push != nullptr selects the push mode: bf16 tiles go to the receive areas of the GPUs that own their rows
   alignas(64) CUtensorMap tmap_a, tmap_w, tmap_out;
+  alignas(64) PushMaps pmaps;
+  memset(&pmaps, 0, sizeof(pmaps));
   int rc = make_tensor_map_2d(&tmap_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, a_codes, k, m, lda, BK, BM);
   if (rc != BFP8_OK) return rc;
   rc = make_tensor_map_2d(&tmap_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, w_codes, k, n, ldw, BK, BN);
   if (rc != BFP8_OK) return rc;
   const bool bf16 = out_dtype == BFP8_OUT_BF16;
-  if (bf16) {
+  if (push != nullptr) {
+    if (!bf16 || inter > 0 || push->world < 2 || push->world > 8 || push->rows <= 0 || push->rows % BM != 0 ||
+        m != static_cast<int64_t>(push->rows) * push->world || n % 64 != 0)
+      return BFP8_ERR_UNSUPPORTED;
+    for (int o = 0; o < push->world; ++o) {
+      // GPU o's receive area: [world][rows][n] bf16, contiguous
+      rc = make_tensor_map_2d(&pmaps.m[o], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, push->recv[o], n,
+                              static_cast<uint64_t>(push->rows) * push->world, n * 2, 64, 32);
+      if (rc != BFP8_OK) return rc;
+    }
+    tmap_out = pmaps.m[push->rank];   // not used by the kernel in this mode
+  } else if (bf16) {
     rc = make_tensor_map_2d(&tmap_out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, out, inter > 0 ? inter : n, m, ldo * 2, 64, 32);
     if (rc != BFP8_OK) return rc;
   } else {
@@ -454,6 +502,17 @@ int launch_gemm_large(const uint8_t* a_codes, int64_t lda, const float* a_scales
   p.status = status_dev;
   p.band = band > 0 ? band : 16;
   p.inter = inter;
+  p.push_world = p.push_rank = p.band_shift = 0;
+  p.push_rows = 1;
+  if (push != nullptr) {
+    p.push_world = push->world;
+    p.push_rank = push->rank;
+    p.push_rows = push->rows;
+    // one band per owner, and every rank starts with a different owner (its own rows come last), so that at
+    // any moment each GPU receives from one peer instead of from all of them
+    p.band = push->rows / BM;
+    p.band_shift = (push->rank + 1) % push->world;
+  }
   const int tiles = p.tiles_m * p.tiles_n;
   int grid = sm_count();
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
@@ -464,7 +523,7 @@ int launch_gemm_large(const uint8_t* a_codes, int64_t lda, const float* a_scales
   static bool done[3][64] = {};
   rc = ensure_smem_limit(kern, kSmemBytes, done[inter > 0 ? 2 : (bf16 ? 1 : 0)]);
   if (rc != BFP8_OK) return rc;
-  kern<<<grid, kThreads, kSmemBytes, st>>>(tmap_a, tmap_w, tmap_out, p);
+  kern<<<grid, kThreads, kSmemBytes, st>>>(tmap_a, tmap_w, tmap_out, pmaps, p);
   BFP8_CUDA_TRY(cudaGetLastError());
   return BFP8_OK;
 }

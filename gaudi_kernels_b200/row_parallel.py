@@ -174,19 +174,67 @@ def reduce_scatter_rows(exchange, partial, bias=None, out=None, out_dtype=None):
     return out
 
 
+def push_supported(m, n, world, partial_dtype=torch.bfloat16):
+    """True where the GEMM can scatter its tiles itself (bfp8_gemm_block128_push)."""
+    return world >= 2 and partial_dtype == torch.bfloat16 and m % (BLOCK * world) == 0 and n % 64 == 0
+
+
 def gemm_k_sharded(a_codes_local, a_scales_local, w_codes_local, w_scales_local, exchange, bias=None,
-                   partial_dtype=torch.bfloat16, out=None):
+                   partial_dtype=torch.bfloat16, out=None, fused=None):
     """Row-parallel GEMM: this rank's K slice in, this rank's rows of the full-K product out.
 
     a_codes_local [M, K_local] / a_scales_local [M, G_local] quantize this rank's activation columns
     (the 1x128 groups never straddle ranks because K slices are whole scale blocks); w_*_local from
-    shard_weight_k.  The partial product is written in `partial_dtype` (bf16 as gk_rank_sum_bf16_v1 sums,
-    or fp32) into the exchange buffer, then reduce_scatter_rows adds the ranks' partials in rank order.
+    shard_weight_k.  Two forms, same rank-order result:
+
+    fused    the GEMM's epilogue stores every bf16 tile into the receive area of the GPU that owns its rows
+             (bfp8_gemm_block128_push), so the exchange overlaps the math; after the barrier each rank holds the
+             `gathered` layout of rank_sum.c and sums it locally.  Needs M % (128 * world) == 0, N % 64 == 0.
+    unfused  the partial is written locally in `partial_dtype` (bf16 or fp32) and reduce_scatter_rows reads the
+             peers' rows over NVLink.  Any shape.
+    fused=None picks the fused form where it applies.
     """
-    from .block_fp8_gemm import gemm_block_fp8
-    m = a_codes_local.shape[0]
+    from .block_fp8_gemm import _group_major, gemm_block_fp8
+    m, k = a_codes_local.shape
     n = w_codes_local.shape[0]
-    partial = exchange.partial(m, n, partial_dtype)
-    gemm_block_fp8(a_codes_local, a_scales_local, w_codes_local, w_scales_local, out=partial, out_dtype=partial_dtype,
-                   check=False)
-    return reduce_scatter_rows(exchange, partial, bias=bias, out=out)
+    world, rank = exchange.world, exchange.rank
+    can_push = push_supported(m, n, world, partial_dtype) and k % 16 == 0
+    if fused is None:
+        fused = can_push
+    if fused and not can_push:
+        raise ValueError("the fused form needs bf16 partials, M % (128 * world) == 0, N % 64 == 0 and K % 16 == 0")
+    if not fused:
+        partial = exchange.partial(m, n, partial_dtype)
+        gemm_block_fp8(a_codes_local, a_scales_local, w_codes_local, w_scales_local, out=partial,
+                       out_dtype=partial_dtype, check=False)
+        return reduce_scatter_rows(exchange, partial, bias=bias, out=out)
+
+    rows = m // world
+    if m * n * 2 > exchange.nbytes:
+        raise ValueError("receive area of %d bytes exceeds the exchange buffer (%d)" % (m * n * 2, exchange.nbytes))
+    g = (k + BLOCK - 1) // BLOCK
+    dev = exchange.device
+    if out is None:
+        out = torch.empty((rows, n), dtype=torch.bfloat16, device=dev)
+    elif tuple(out.shape) != (rows, n) or out.dtype != torch.bfloat16 or not out.is_contiguous():
+        raise ValueError("out must be a contiguous bf16 [M / world, N] tensor")
+    if bias is not None:
+        if bias.numel() != n:
+            raise ValueError("bias with N elements required")
+        bias = bias.to(device=dev, dtype=torch.float32).contiguous().view(-1)
+    lib = exchange.lib
+    with torch.cuda.device(dev):
+        sa, ldsa = _group_major(a_scales_local, m, g)
+        recv = (ctypes.c_void_p * world)(*exchange.ptrs)
+        rc = lib.bfp8_gemm_block128_push(
+            a_codes_local.data_ptr(), a_codes_local.stride(0), sa.data_ptr(), ldsa, w_codes_local.data_ptr(),
+            w_codes_local.stride(0), w_scales_local.data_ptr(), recv, rank, world, m, n, k,
+            exchange.status.data_ptr() + 8, _stream_ptr())
+        _lib.check(rc, "bfp8_gemm_block128_push")
+        exchange.barrier()                                   # every rank's tiles have landed here
+        slices = (ctypes.c_void_p * world)(*[exchange.ptrs[rank] + r * rows * n * 2 for r in range(world)])
+        rc = lib.bfp8_rank_sum_slices(slices, out.data_ptr(), rows * n, world, _lib.OUT_BF16,
+                                      bias.data_ptr() if bias is not None else None, n, _stream_ptr())
+        _lib.check(rc, "bfp8_rank_sum_slices")
+        exchange.barrier()                                   # the receive area may be overwritten again
+    return out

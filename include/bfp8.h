@@ -210,6 +210,21 @@ int bfp8_rank_sum(const void* gathered, void* dst, int64_t elems, int world_size
 int bfp8_rank_sum_slices(const void* const* slices, void* dst, int64_t elems, int world_size, int dtype,
                          const float* bias, int64_t bias_period, void* stream);
 
+/* Row-parallel (K-sharded) GEMM whose epilogue scatters the result: this rank's partial product
+ * A[:, K_r] . W[:, K_r]^T is rounded to bf16 and every 128-row tile is stored - by the same bulk tensor store the
+ * ordinary kernel uses, over NVLink where the destination is another GPU - into the receive area of the rank
+ * that owns those rows, so the transfer runs under the remaining tiles' math.  recv is a HOST array of world_size
+ * device pointers; recv[o] is rank o's receive area, bf16 [world_size][m / world_size][n] contiguous (peer
+ * memory from bfp8_peer_open for o != rank), and this rank's rows [o R, (o + 1) R), R = m / world_size, land in
+ * recv[o][rank].  After a bfp8_peer_barrier, recv[rank] is exactly the `gathered` operand of bfp8_rank_sum
+ * (csrc/tpc/generic_dense/rank_sum.c:2: world_size contiguous slices).  Requires m % (128 * world_size) == 0 and
+ * n % 64 == 0 (BFP8_ERR_UNSUPPORTED otherwise; use bfp8_gemm_block128 + bfp8_rank_sum_slices then); no bias
+ * here - add it in the sum.  No TMA load of this kernel touches peer memory and nothing is multicast. */
+int bfp8_gemm_block128_push(const uint8_t* a_codes, int64_t lda, const float* a_scales, int64_t ldsa,
+                            const uint8_t* w_codes, int64_t ldw, const float* w_scales,
+                            void* const* recv, int rank, int world_size,
+                            int64_t m, int64_t n, int64_t k, uint32_t* status_dev, void* stream);
+
 /* Device memory that other processes on the same machine can map (one process per GPU).  These have no
  * counterpart in the reference, whose cross-device exchange lives in the external runtime
  * (csrc/tpc/generic_dense/rank_sum.c:2 only sees gathered data).

@@ -46,9 +46,17 @@ def _worker(rank, world, port, m, k, n, partial_name, use_bias, result_queue):
         outs = []
         for _ in range(3):                                                   # the buffer is reused call after call
             outs.append(rp.gemm_k_sharded(a_codes, a_scales, w_loc, s_loc, ex, bias=bias, partial_dtype=partial_dtype))
+        fused = rp.push_supported(m, n, world, partial_dtype)
+        if fused:
+            # the same product with the exchange done by the sum kernel instead of the GEMM's epilogue: same bits
+            outs.append(rp.gemm_k_sharded(a_codes, a_scales, w_loc, s_loc, ex, bias=bias, partial_dtype=partial_dtype,
+                                          fused=False))
+        else:
+            with pytest.raises(ValueError):
+                rp.gemm_k_sharded(a_codes, a_scales, w_loc, s_loc, ex, bias=bias, partial_dtype=partial_dtype, fused=True)
         torch.cuda.synchronize()
         assert not ex.timed_out()
-        assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+        assert all(torch.equal(outs[0], o) for o in outs[1:])
         r0, r1 = rp.row_bounds(m, world, rank)
         got = outs[0].cpu()
         assert tuple(got.shape) == (r1 - r0, n) and got.dtype == partial_dtype
@@ -74,7 +82,7 @@ def _worker(rank, world, port, m, k, n, partial_name, use_bias, result_queue):
         assert close <= 1e-2 * rms * world + (world + 1) * step, close
         ex.close()
         dist.destroy_process_group()
-        result_queue.put((rank, "ok", err / rms))
+        result_queue.put((rank, "ok", (err / rms, fused)))
     except Exception as e:                                                   # noqa: BLE001 - reported to the parent
         import traceback
         result_queue.put((rank, "fail", traceback.format_exc() + repr(e)))
@@ -103,3 +111,4 @@ def test_row_parallel_gemm_two_gpus(m, k, n, partial, bias):
     assert sorted(r[0] for r in results) == [0, 1]
     for rank, state, info in results:
         assert state == "ok", "rank %d: %s" % (rank, info)
+        assert info[1] == (partial == "bfloat16" and m % 256 == 0 and n % 64 == 0)     # which form ran
