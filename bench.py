@@ -44,6 +44,7 @@ WORKLOADS = {
     "ffn70b": (16384, 8192, 28672),
     "prefill_up_quarter": (2048, 4096, 14336),     # same kernel and K/N, a quarter of the rows: the size used for ncu captures
     "prefill_up_token_channel": (8192, 4096, 14336),   # same shape, per-token / per-channel scales (no per-block promotion)
+    "ffn70b_down": (16384, 28672, 8192),           # row-parallel: W split on K, rank-order sum over peer memory (N > 1 only)
     "codec": (8192, 8192, 0),                      # the elementwise codec configuration, fp32 [8192, 8192] (no GEMM)
 }
 METRIC = "block_fp8_gemm_tflops"
@@ -291,6 +292,85 @@ def bench_checkpoint_stream(torch, device, tensors=12, n=8192, k=8192):
             "source": "pinned host memory"}
 
 
+def run_row_parallel(args, torch, dist, gk, device, workload, m, k, n, world, rank):
+    """K-sharded down projection: every rank multiplies its K slice and the partials are added in rank order.
+
+    Operands are drawn directly as codes (the quantizers are timed elsewhere).  A step is the fused form:
+    GEMM whose epilogue stores its bf16 tiles into the owning GPU's memory, barrier, local rank-order sum, barrier.
+    The unfused form (local partial, then a sum kernel that reads the peers' rows) is timed beside it.
+    """
+    from gaudi_kernels_b200 import row_parallel as rp
+    if world < 2:
+        raise SystemExit("ffn70b_down is a multi-GPU workload: start it with torch.distributed.run and --gpus N >= 2")
+    k0, k1 = rp.k_shard_bounds(k, world, rank)
+    kl = k1 - k0
+    g = torch.Generator(device=device).manual_seed(17 + rank)
+    a_codes = torch.randint(0, 0x77, (m, kl), generator=g, device=device, dtype=torch.uint8)
+    a_scales = torch.rand((kl // 128, m), generator=g, device=device).t()
+    w_codes = torch.randint(0, 0x77, (n, kl), generator=g, device=device, dtype=torch.uint8)
+    w_scales = torch.rand((n // 128, kl // 128), generator=g, device=device) * 1e-3
+    ex = rp.PeerExchange(m * n * 2)
+    r0, r1 = rp.row_bounds(m, world, rank)
+    out = torch.empty((r1 - r0, n), dtype=torch.bfloat16, device=device)
+    flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=device)
+    fused = rp.push_supported(m, n, world)
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            flush.zero_()
+            fn()
+        dist.barrier()
+        torch.cuda.synchronize()
+        ms = []
+        for _ in range(steps):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            ms.append((e0, e1))
+        dist.barrier()
+        torch.cuda.synchronize()
+        total = torch.tensor([sum(a.elapsed_time(b) for a, b in ms)], dtype=torch.float64, device=device)
+        dist.all_reduce(total, op=dist.ReduceOp.MAX)
+        return float(total.item()) / steps
+
+    sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", 0)))
+    if rank == 0:
+        sampler.start()
+    ms = timed(lambda: rp.gemm_k_sharded(a_codes, a_scales, w_codes, w_scales, ex, out=out, fused=fused),
+               args.steps, max(args.warmup, 3))
+    clocks = sampler.stop() if rank == 0 else None
+    ms_unfused = timed(lambda: rp.gemm_k_sharded(a_codes, a_scales, w_codes, w_scales, ex, out=out, fused=False),
+                       min(args.steps, 10), 3)
+    local = ex.partial(m, n, torch.bfloat16)
+    ms_gemm = timed(lambda: gk.gemm_block_fp8(a_codes, a_scales, w_codes, w_scales, out=local, check=False),
+                    min(args.steps, 10), 3)
+    timed_out = ex.timed_out()
+    ex.close()
+    if rank == 0:
+        flops = 2.0 * m * k * n
+        peak_tflops, peak_how, _ = measured_peaks()
+        line = {"metric": METRIC, "value": flops / (ms * 1e-3) / 1e12, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+                "vs_baseline": None, "dtype": "e4m3 x e4m3 -> f32, bf16 partials, fp32 rank-order sum (bf16 out)",
+                "data": "synthetic",
+                "config": {"workload": "%s M=%d K=%d N=%d" % (workload, m, k, n),
+                           "sharding": "W and A split on K over %d ranks; rank r keeps output rows [r M / W, (r + 1) M / W)" % world,
+                           "form": "fused: tiles stored to the owning GPU by the GEMM epilogue" if fused else "unfused",
+                           "l2": "256 MiB buffer rewritten between timed steps",
+                           "timed": "GEMM + inter-GPU barrier + rank-order sum + barrier, operands resident in HBM"},
+                "roofline": {"bound": "tensor", "achieved": flops / world / (ms * 1e-3) / 1e12, "peak": peak_tflops,
+                             "unit": "TFLOP/s", "frac": flops / world / (ms * 1e-3) / 1e12 / peak_tflops,
+                             "peak_source": peak_how + " - of measured", "traffic": None,
+                             "kernel": "gemm_block128_kernel<bf16 out> (push mode) + rank_sum_kernel"},
+                "compare": {"unfused_ms_per_step": ms_unfused, "local_gemm_only_ms": ms_gemm,
+                            "nvlink_bytes_into_each_gpu": (world - 1) * (m // world) * n * 2},
+                "clocks": clocks, "gpu_launches": 4 * args.steps, "barrier_wait_expired": timed_out}
+        print(json.dumps(line), flush=True)
+    dist.destroy_process_group()
+
+
 def make_problem(torch, gk, m, k, n_local, n_offset, n_total, device, seed=0):
     """Synthetic operands: bf16 activations and an fp32 weight slice, quantized on the GPU by the library."""
     g = torch.Generator(device="cpu").manual_seed(seed)
@@ -374,6 +454,10 @@ def main():
     import gaudi_kernels_b200 as gk
     from gaudi_kernels_b200 import _lib
     lib = _lib.load()
+
+    if workload == "ffn70b_down":
+        run_row_parallel(args, torch, dist, gk, device, workload, m, k, n, world, rank)
+        return
 
     if workload == "codec":
         # codec kernels only (single GPU; every rank would do identical work)
