@@ -398,6 +398,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   __syncthreads();
   cluster_sync_all();                               // the peer may still read this CTA's shared memory or barriers
   ptx::tc_fence_after_sync();
+  ptx::idle_after_abort(abort_flag);
   if (warp == kEpiWarps + 1) tmem_dealloc_pair(tmem_base, kTmemCols);
   if (threadIdx.x == 0 && tail->abort_flag != 0) atomicOr(p.status, BFP8_STATUS_WAIT_TIMEOUT);
 }

@@ -371,6 +371,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   ptx::tc_fence_before_sync();
   __syncthreads();
   ptx::tc_fence_after_sync();
+  ptx::idle_after_abort(abort_flag);
   if (warp == kEpiWarps + 1) ptx::tmem_dealloc(tmem_base, C::kTmemCols);
   if (threadIdx.x == 0 && tail->abort_flag != 0) atomicOr(p.status, BFP8_STATUS_WAIT_TIMEOUT);
 }

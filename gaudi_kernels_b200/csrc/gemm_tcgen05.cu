@@ -404,6 +404,7 @@ gemm_block128_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   ptx::tc_fence_before_sync();
   __syncthreads();
   ptx::tc_fence_after_sync();
+  ptx::idle_after_abort(abort_flag);
   if (warp == kEpiWarps + 1) ptx::tmem_dealloc(tmem_base, kTmemCols);
   if (threadIdx.x == 0 && tail->abort_flag != 0) atomicOr(p.status, BFP8_STATUS_WAIT_TIMEOUT);
 }

@@ -42,6 +42,15 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
+// A CTA whose bounded wait expired leaves with copies into its shared memory and MMAs into its TMEM possibly
+// still in flight; nothing tracks them any more.  Before shared memory and TMEM are given up the CTA therefore
+// idles for about 100 us, orders of magnitude longer than any single bulk copy or MMA takes to land.
+__device__ __forceinline__ void idle_after_abort(volatile uint32_t* abort_flag) {
+  if (*abort_flag == 0) return;
+  const long long t0 = clock64();
+  while (clock64() - t0 < 200000LL) __nanosleep(1000);
+}
+
 // Cluster-wide barrier, split in two so that work can be placed between arriving and waiting.  Every thread
 // of every CTA in the cluster takes part; release / acquire order shared-memory writes across the CTAs.
 __device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release;" ::: "memory"); }

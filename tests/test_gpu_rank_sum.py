@@ -92,3 +92,34 @@ def test_single_rank_exchange_and_barrier(lib):
     finally:
         if created:
             dist.destroy_process_group()
+
+
+def test_barrier_wait_expires_with_a_status_not_a_hang(lib):
+    """Failure detection on the device: a rank that never arrives makes the bounded wait run out; the kernel
+    raises BFP8_STATUS_WAIT_TIMEOUT and returns, and the context stays usable.  The absent rank is simply a flag
+    array nothing writes to (no second process, no fault)."""
+    import time
+    from gaudi_kernels_b200 import _lib
+    mine = torch.zeros(8, dtype=torch.int32, device="cuda")
+    absent = torch.zeros(8, dtype=torch.int32, device="cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    flags = (ctypes.c_void_p * 2)(mine.data_ptr(), absent.data_ptr())
+    stream = torch.cuda.current_stream().cuda_stream
+    t0 = time.perf_counter()
+    rc = lib.bfp8_peer_barrier(flags, 0, 2, 1, 2_000_000, status.data_ptr() + 8, stream)      # about a millisecond
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert time.perf_counter() - t0 < 5.0
+    assert int(status.cpu()[2]) & _lib.STATUS_WAIT_TIMEOUT
+    assert int(absent.cpu()[0]) == 1 and int(mine.cpu()[0]) == 1        # this rank did publish its epoch to both
+    # when the other rank has arrived (its flag is set), the same call completes without the status bit
+    status.zero_()
+    mine[1] = 2
+    assert lib.bfp8_peer_barrier(flags, 0, 2, 2, 2_000_000, status.data_ptr() + 8, stream) == 0
+    torch.cuda.synchronize()
+    assert int(status.cpu()[2]) == 0
+    # host-visible argument errors launch nothing
+    assert lib.bfp8_peer_barrier(flags, 2, 2, 1, 0, status.data_ptr() + 8, stream) == -3
+    assert lib.bfp8_peer_barrier(flags, 0, 9, 1, 0, status.data_ptr() + 8, stream) == -3
+    x = torch.arange(8, device="cuda")
+    assert int(x.sum()) == 28                                           # the context still works
