@@ -263,6 +263,28 @@ def gemm_block_fp8_swiglu(a_codes, a_scales, w_codes, w_scales, bias=None, out=N
     return out
 
 
+def silu_and_mul(gate_up, out=None):
+    """bf16 [rows, 2 * I] (gate columns, then up columns) -> bf16 [rows, I] = silu(gate) * up.
+
+    gk_silu_and_mul_bf16_v1 (csrc/tpc/generic_dense/silu_and_mul_bf16.c:16) as a stand-alone kernel, for GEMM
+    results of the small-M schedule; gemm_block_fp8_swiglu fuses the same step for large M.
+    """
+    if (not isinstance(gate_up, torch.Tensor) or gate_up.dtype != torch.bfloat16 or gate_up.ndim != 2
+            or gate_up.shape[1] % 2 or not gate_up.numel() or gate_up.stride(1) != 1 or gate_up.device.type != "cuda"):
+        raise ValueError("expected a nonempty bf16 [rows, 2 * I] CUDA tensor with unit column stride")
+    rows, inter = gate_up.shape[0], gate_up.shape[1] // 2
+    if out is None:
+        out = torch.empty((rows, inter), dtype=torch.bfloat16, device=gate_up.device)
+    elif (out.dtype != torch.bfloat16 or tuple(out.shape) != (rows, inter) or out.stride(1) != 1
+          or out.device != gate_up.device):
+        raise ValueError("out must be bf16 [rows, I] with unit column stride on the input's device")
+    with torch.cuda.device(gate_up.device):
+        rc = _lib.load().bfp8_silu_and_mul_bf16(gate_up.data_ptr(), gate_up.stride(0), out.data_ptr(), out.stride(0),
+                                                rows, inter, _stream_ptr())
+    _lib.check(rc, "bfp8_silu_and_mul_bf16")
+    return out
+
+
 def reference(x, weight, scales, *, native_half=False, bias=None, out_dtype=torch.bfloat16, out=None):
     """Drop-in for gaudi_kernels.block_fp8_oracle.reference, computed on the GPU.
 

@@ -160,6 +160,61 @@ extern "C" int bfp8_gemm_block128_swiglu(const uint8_t* a_codes, int64_t lda, co
                            /*push=*/nullptr, static_cast<cudaStream_t>(stream));
 }
 
+// ---- the SwiGLU step on its own, for results of the schedules that have no fused form (decode bucket) -------
+
+namespace {
+// Same arithmetic as the fused epilogue of gemm_tcgen05.cu (silu_and_mul_bf16.c:4-13).
+__device__ __forceinline__ float silu_mul_f32(float g, float u) {
+  const float q = __fdividef(g, 1.0f + __expf(-g));
+  return (g <= -88.0f ? 0.0f : q) * u;
+}
+
+// One 16-byte vector (8 outputs) per thread and iteration; gate at column c, up at column c + inter of a row.
+__global__ void __launch_bounds__(256)
+silu_and_mul_kernel(const uint16_t* __restrict__ gate_up, int64_t ld_in, uint16_t* __restrict__ out, int64_t ld_out,
+                    int64_t rows, int64_t inter, int vec_ok) {
+  if (vec_ok) {
+    const int64_t vecs = inter >> 3, total = rows * vecs;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+      const int64_t r = i / vecs, v = i - r * vecs;
+      const uint4 g = __ldcs(reinterpret_cast<const uint4*>(gate_up + r * ld_in) + v);
+      const uint4 u = __ldcs(reinterpret_cast<const uint4*>(gate_up + r * ld_in + inter) + v);
+      const uint32_t* gw = reinterpret_cast<const uint32_t*>(&g);
+      const uint32_t* uw = reinterpret_cast<const uint32_t*>(&u);
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        o[j] = pack_bf16x2(silu_mul_f32(bf16_lo_to_float(gw[j]), bf16_lo_to_float(uw[j])),
+                           silu_mul_f32(bf16_hi_to_float(gw[j]), bf16_hi_to_float(uw[j])));
+      __stcs(reinterpret_cast<uint4*>(out + r * ld_out) + v, make_uint4(o[0], o[1], o[2], o[3]));
+    }
+  } else {
+    const int64_t total = rows * inter;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+      const int64_t r = i / inter, c = i - r * inter;
+      const float g = bf16_bits_to_float(gate_up[r * ld_in + c]), u = bf16_bits_to_float(gate_up[r * ld_in + inter + c]);
+      out[r * ld_out + c] = static_cast<uint16_t>(float_to_bf16_bits(silu_mul_f32(g, u)));
+    }
+  }
+}
+}  // namespace
+
+extern "C" int bfp8_silu_and_mul_bf16(const uint16_t* gate_up, int64_t ld_in, uint16_t* out, int64_t ld_out,
+                                      int64_t rows, int64_t inter, void* stream) {
+  if (!gate_up || !out) return BFP8_ERR_NULL;
+  if (rows <= 0 || inter <= 0 || ld_in < 2 * inter || ld_out < inter || rows > (1LL << 40) / inter) return BFP8_ERR_SHAPE;
+  if (!aligned(gate_up, 2) || !aligned(out, 2)) return BFP8_ERR_ALIGN;
+  const int vec = aligned(gate_up, 16) && aligned(out, 16) && inter % 8 == 0 && ld_in % 8 == 0 && ld_out % 8 == 0;
+  const int64_t work = vec ? rows * (inter / 8) : rows * inter;
+  const int64_t want = (work + 255) / 256, cap = static_cast<int64_t>(sm_count()) * 8;
+  silu_and_mul_kernel<<<static_cast<int>(want < cap ? want : cap), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      gate_up, ld_in, out, ld_out, rows, inter, vec);
+  BFP8_CUDA_TRY(cudaGetLastError());
+  return BFP8_OK;
+}
+
 // ---- row-parallel GEMM whose epilogue scatters its tiles to the GPUs that reduce them -------------------
 
 extern "C" int bfp8_gemm_block128_push(const uint8_t* a_codes, int64_t lda, const float* a_scales, int64_t ldsa,

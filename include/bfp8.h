@@ -196,6 +196,14 @@ int bfp8_gemm_block128_swiglu(const uint8_t* a_codes, int64_t lda, const float* 
                               const float* bias, void* out, int64_t ldo,
                               int64_t m, int64_t inter, int64_t k, uint32_t* status_dev, void* stream);
 
+/* The SwiGLU step on its own: out[r, c] = bf16( silu(gate_up[r, c]) * gate_up[r, inter + c] ), bf16 in and out.
+ * Replaces gk_silu_and_mul_bf16_v1 (csrc/tpc/generic_dense/silu_and_mul_bf16.c:16-75, input [rows, 2 * inter], glue
+ * csrc/host/generic_dense_glue.cpp:196-216) for GEMM results of the schedules that have no fused epilogue (the
+ * decode bucket); same arithmetic as bfp8_gemm_block128_swiglu.  Any inter; 16-byte vector path when inter and both
+ * leading dimensions are multiples of 8. */
+int bfp8_silu_and_mul_bf16(const uint16_t* gate_up, int64_t ld_in, uint16_t* out, int64_t ld_out,
+                           int64_t rows, int64_t inter, void* stream);
+
 /* Sum of world_size per-rank slices in canonical rank order: dst[i] = ((s0[i] + s1[i]) + s2[i]) + ... in fp32,
  * rounded once (RNE) for bf16 data.  Replaces gk_rank_sum_bf16_v1 / gk_rank_sum_f32_v1
  * (csrc/tpc/generic_dense/rank_sum.c:4-42; glue csrc/host/generic_dense_glue.cpp:569-600): `gathered` holds the

@@ -117,3 +117,34 @@ def test_swiglu_rejects_bad_arguments(gk):
         gk.gemm_block_fp8_swiglu(a_codes, a_scales, w, torch.ones((3, 1), device="cuda"))
     with pytest.raises(ValueError):
         gk.gemm_block_fp8_swiglu(a_codes, a_scales, w, torch.ones((2, 1), device="cuda"), bias=torch.zeros(100))
+
+
+@pytest.mark.parametrize("rows,inter", [(1, 14336), (8, 7168), (64, 14336), (5, 100), (3, 7), (2048, 1024)])
+def test_standalone_silu_and_mul_matches_restatement(gk, rows, inter):
+    g = torch.Generator().manual_seed(rows + inter)
+    x = (torch.randn((rows, 2 * inter), generator=g) * 6).to(torch.bfloat16)
+    x[0, 0] = -100.0                                   # silu is exactly 0 at and below -88
+    x[0, inter] = 3.0
+    if inter > 2:
+        x[0, 1] = float("nan")                         # NaN gate passes through
+        x[0, 2] = 90.0
+    want = swiglu_ref.silu_and_mul_bf16(x)
+    canvas = torch.full((rows + 1, inter + 8), 7.0, dtype=torch.bfloat16, device="cuda")
+    got = gk.silu_and_mul(x.cuda(), out=canvas[:rows, :inter]).cpu()
+    assert bool((canvas[rows:] == 7.0).all()) and bool((canvas[:, inter:] == 7.0).all())
+    finite = ~torch.isnan(want)
+    assert torch.equal(torch.isnan(got), torch.isnan(want))
+    diff = (got.double() - want.double()).abs()[finite]
+    assert bool((diff <= _bf16_step(want)[finite] + 1e-36).all())
+    assert float((got[finite] != want[finite]).float().mean()) < 0.01
+    assert float(got[0, 0]) == 0.0
+    # the fused and the stand-alone kernel share the arithmetic: GEMM -> silu_and_mul equals the fused GEMM bit for bit
+    if rows == 64:
+        m, k, i2 = 64, 512, 256
+        xg, codes, s, b = _problem(m, k, i2, seed=3, bias=True)
+        a_codes, a_scales = gk.quantize_act_1x128(xg.cuda(), native_half=True)
+        w_plain, s_plain = gk.prepare_weight(codes.cuda(), s.cuda(), native_half=True)
+        two_step = gk.silu_and_mul(gk.gemm_block_fp8(a_codes, a_scales, w_plain, s_plain, bias=b.cuda(), schedule=1))
+        w_il, s_il = gk.prepare_weight_swiglu(codes.cuda(), s.cuda(), native_half=True)
+        fused = gk.gemm_block_fp8_swiglu(a_codes, a_scales, w_il, s_il, bias=b.cuda())
+        assert torch.equal(two_step, fused)
