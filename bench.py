@@ -639,10 +639,12 @@ def main():
         t0 = time.perf_counter()
         yb = block_fp8_ref.reference(xs, wc, sc, native_half=True)
         dt = time.perf_counter() - t0
-        if dt < 5.0 and rows < m:
-            # the first sample was short (its time is mostly weight preparation): size a second one for about
+        for _ in range(3):
+            if dt >= 5.0 or rows >= m:
+                break
+            # the sample was short (a small sample's time is mostly weight preparation): grow it towards about
             # ten seconds of host work, so that the per-row cost dominates the figure
-            rows = int(min(m, max(rows, rows * 10.0 / dt))) // 32 * 32 or rows
+            rows = int(min(m, max(2 * rows, rows * 10.0 / dt))) // 32 * 32 or rows
             xs = x[:rows].contiguous()
             t0 = time.perf_counter()
             yb = block_fp8_ref.reference(xs, wc, sc, native_half=True)

@@ -34,6 +34,7 @@ def _workspace(dev, nbytes):
 
 
 _HOST_ROW_BLOCK = 1024          # reference() on host tensors pipelines blocks of at least this many rows
+_HOST_MAX_BLOCKS = 8            # finer blocks change nothing: the copy back to the host is the bound
 _copy_streams = {}
 
 
@@ -346,7 +347,7 @@ def reference(x, weight, scales, *, native_half=False, bias=None, out_dtype=torc
             # Host tensors: the result (2 bytes per output) is larger than the inputs, so its copy back to the
             # host dominates.  Rows are processed in blocks and each block's result is copied on a second
             # stream while the next block is uploaded and multiplied (the two copy directions overlap).
-            blocks = 1 if m < 2 * _HOST_ROW_BLOCK else min(8, m // _HOST_ROW_BLOCK)
+            blocks = 1 if m < 2 * _HOST_ROW_BLOCK else min(_HOST_MAX_BLOCKS, m // _HOST_ROW_BLOCK)
             rows_per = ((m + blocks - 1) // blocks + BLOCK - 1) // BLOCK * BLOCK
             main = torch.cuda.current_stream()
             side = _copy_stream(dev)
