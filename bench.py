@@ -44,6 +44,7 @@ WORKLOADS = {
     "ffn70b": (16384, 8192, 28672),
     "prefill_up_quarter": (2048, 4096, 14336),     # same kernel and K/N, a quarter of the rows: the size used for ncu captures
     "prefill_up_token_channel": (8192, 4096, 14336),   # same shape, per-token / per-channel scales (no per-block promotion)
+    "decode_m64": (64, 4096, 14336),               # the decode bucket's largest M: the weight-streaming schedule, HBM-bound
     "ffn70b_down": (16384, 28672, 8192),           # row-parallel: W split on K, rank-order sum over peer memory (N > 1 only)
     "codec": (8192, 8192, 0),                      # the elementwise codec configuration, fp32 [8192, 8192] (no GEMM)
 }
@@ -225,7 +226,7 @@ def bench_codec(torch, lib, device, steps, warmup):
     return out
 
 
-def bench_decode_bucket(torch, lib, device, k=4096, n=14336, reps=20, rounds=8):
+def bench_decode_bucket(torch, lib, device, k=4096, n=14336, reps=20, rounds=8, ms=(1, 8, 32, 64)):
     """Small-M GEMM (the decode bucket) at one weight shape: HBM-bound on the 58.7 MB of weight codes.
 
     The weight fits in L2, so launches rotate over four weight copies; `reps` launches are captured in one CUDA
@@ -236,7 +237,7 @@ def bench_decode_bucket(torch, lib, device, k=4096, n=14336, reps=20, rounds=8):
     w_scales = torch.rand((n // 128, k // 128), generator=g, device=device) * 1e-3
     status = torch.zeros(4, dtype=torch.int32, device=device)
     out = {}
-    for m in (1, 8, 32, 64):
+    for m in ms:
         a_codes = torch.randint(0, 0x77, (m, k), generator=g, device=device, dtype=torch.uint8)
         a_scales = torch.rand((k // 128, m), generator=g, device=device)
         y = torch.empty((m, n), dtype=torch.bfloat16, device=device)
@@ -266,7 +267,8 @@ def bench_decode_bucket(torch, lib, device, k=4096, n=14336, reps=20, rounds=8):
             ts.append(e0.elapsed_time(e1) / reps)
         us = statistics.median(ts) * 1e3
         nbytes = n * k + 4 * (n // 128) * (k // 128) + m * k + 4 * m * (k // 128) + 2 * m * n
-        out["M=%d" % m] = {"us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1), "tflops": round(2.0 * m * n * k / us / 1e6, 1)}
+        out["M=%d" % m] = {"us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1), "tflops": round(2.0 * m * n * k / us / 1e6, 1),
+                           "bytes": nbytes}
     return out
 
 
@@ -459,6 +461,29 @@ def main():
 
     if workload == "ffn70b_down":
         run_row_parallel(args, torch, dist, gk, device, workload, m, k, n, world, rank)
+        return
+
+    if workload == "decode_m64":
+        # the decode bucket: a launch is shorter than the host's launch path, so launches are timed inside a CUDA
+        # graph (20 per replay, four rotating weight copies: W always comes from DRAM), not one event pair each
+        if rank == 0:
+            rounds = max(args.steps, 8)
+            res = bench_decode_bucket(torch, lib, device, k, n, reps=20, rounds=rounds, ms=(m,))["M=%d" % m]
+            _, _, hbm_gbs = measured_peaks()
+            line = {"metric": METRIC, "value": res["tflops"], "unit": UNIT, "n_gpus": 1, "steps": 20 * rounds,
+                    "warmup": 4, "ms_per_step": res["us"] * 1e-3, "higher_is_better": True, "scaling": "weak",
+                    "vs_baseline": None, "dtype": "e4m3 x e4m3 -> f32 (bf16 out)", "data": "synthetic",
+                    "config": {"workload": "%s M=%d K=%d N=%d" % (workload, m, k, n),
+                               "l2": "launches rotate over four copies of W (235 MB, larger than L2)",
+                               "timed": "CUDA graph of 20 launches per replay, median over replays"},
+                    "roofline": {"bound": "hbm", "achieved": res["gbs"], "peak": hbm_gbs, "unit": "GB/s",
+                                 "frac": res["gbs"] / hbm_gbs, "peak_source": "MEASURED_PEAKS.json hbm_gbs - of measured",
+                                 "traffic": profiled_traffic(workload), "kernel": "gemm_smallm_kernel<MP=64>",
+                                 "algorithmic_bytes": res["bytes"]},
+                    "gpu_launches": 20 * rounds}
+            print(json.dumps(line), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
         return
 
     if workload == "codec":
