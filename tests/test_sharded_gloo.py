@@ -86,3 +86,51 @@ def test_row_parallel_bounds_cover_everything_once():
             assert all(a[1] == b[0] for a, b in zip(rows, rows[1:]))
     with pytest.raises(ValueError):
         k_shard_bounds(1024, 4, 4)
+
+
+def _row_parallel_worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from gaudi_kernels_b200 import row_parallel as rp
+        from oracle import block_fp8_ref, fp8_codec_ref, rank_sum_ref
+        rng = np.random.default_rng(1)                       # same inputs on every rank
+        m, k, n = 8, 640, 256                                # 5 scale blocks of K over 2 ranks: 3 + 2
+        x = torch.from_numpy(rng.standard_normal((m, k), dtype=np.float32)).to(torch.bfloat16)
+        codes, scales = fp8_codec_ref.quantize_block128(rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02))
+        w = torch.from_numpy(codes).view(torch.float8_e4m3fn)
+        s = torch.from_numpy(scales)
+        k0, k1 = rp.k_shard_bounds(k, world, rank)
+        w_loc, s_loc = rp.shard_weight_k(w, s, world, rank)
+        assert tuple(w_loc.shape) == (n, k1 - k0) and tuple(s_loc.shape) == (n // 128, (k1 - k0) // 128)
+        assert torch.equal(w_loc.view(torch.uint8), w.view(torch.uint8)[:, k0:k1])
+        # this rank's partial over its K slice, in both precisions the sum kernel takes
+        y64, ybf = block_fp8_ref.reference_rows(x[:, k0:k1].contiguous(), w_loc, s_loc, native_half=True)
+        full64, _ = block_fp8_ref.reference_rows(x, w, s, native_half=True)
+        rms = float(full64.pow(2).mean().sqrt())
+        for part in (ybf, y64.float()):
+            # what the runtime's all-gather hands to rank_sum: world slices back to back, in rank order
+            gathered = torch.empty((world,) + tuple(part.shape), dtype=part.dtype)
+            dist.all_gather_into_tensor(gathered.view(world * m, n), part.contiguous())
+            total = rank_sum_ref.rank_sum(gathered.reshape(-1), world).view(m, n)
+            # the 1x128 groups never straddle ranks, so the K-sharded sum is the full product up to rounding
+            tol = 1e-5 * rms if part.dtype == torch.float32 else 2.0 ** -7 * float(full64.abs().max()) * (world + 1)
+            assert float((total.double() - full64).abs().max()) <= tol
+            r0, r1 = rp.row_bounds(m, world, rank)
+            mine = total[r0:r1]                              # the rows this rank keeps after the reduce-scatter
+            rows = [torch.empty((rp.row_bounds(m, world, r)[1] - rp.row_bounds(m, world, r)[0], n), dtype=part.dtype)
+                    for r in range(world)]
+            dist.all_gather(rows, mine.contiguous())
+            assert torch.equal(torch.cat(rows), total)
+        open(os.path.join(out_dir, "rp%d" % rank), "w").write("ok")
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_row_parallel_logic(tmp_path):
+    """K sharding + rank-order sum on CPU: two gloo ranks, oracle partials, restated rank_sum, full-K oracle."""
+    world = 2
+    mp.spawn(_row_parallel_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    assert all((tmp_path / ("rp%d" % r)).exists() for r in range(world))
