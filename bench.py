@@ -272,6 +272,71 @@ def bench_decode_bucket(torch, lib, device, k=4096, n=14336, reps=20, rounds=8, 
     return out
 
 
+def bench_decode_ffn(torch, lib, device, hidden=4096, inter=14336, reps=10, rounds=8):
+    """One FFN of a decode step, five kernels back to back: 1x128 quantize -> gate GEMM and up GEMM into the two halves
+    of one [M, 2 I] buffer -> silu_and_mul fused into the 1x128 quantizer -> down GEMM [M, hidden].  Gate and up are separate
+    launches of I = 14336 columns each (112 tiles: one CTA per tile, no partial sums) rather than one of 28672.
+    Captured `reps` times in a CUDA graph over two rotating sets of weights (352 MB, larger than L2); all kernels are
+    launched with programmatic stream serialization, so each one's launch and set-up overlap the tail of the one
+    before.  HBM-bound on the 176 MB of weight codes per FFN."""
+    g = torch.Generator(device=device).manual_seed(9)
+    sets = []
+    for _ in range(2):
+        sets.append((torch.randint(0, 0x77, (2 * inter, hidden), generator=g, device=device, dtype=torch.uint8),
+                     torch.rand((2 * inter // 128, hidden // 128), generator=g, device=device) * 1e-3,
+                     torch.randint(0, 0x77, (hidden, inter), generator=g, device=device, dtype=torch.uint8),
+                     torch.rand((hidden // 128, inter // 128), generator=g, device=device) * 1e-3))
+    status = torch.zeros(4, dtype=torch.int32, device=device)
+    out = {}
+    for m in (1, 8, 64):
+        x = torch.randn((m, hidden), generator=g, device=device).to(torch.bfloat16)
+        a1 = torch.empty((m, hidden), dtype=torch.uint8, device=device)
+        s1 = torch.empty((hidden // 128, m), dtype=torch.float32, device=device)
+        gu = torch.empty((m, 2 * inter), dtype=torch.bfloat16, device=device)
+        a2 = torch.empty((m, inter), dtype=torch.uint8, device=device)
+        s2 = torch.empty((inter // 128, m), dtype=torch.float32, device=device)
+        y = torch.empty((m, hidden), dtype=torch.bfloat16, device=device)
+        ws_bytes = max(lib.bfp8_gemm_block128_workspace_bytes(m, 2 * inter, hidden),
+                       lib.bfp8_gemm_block128_workspace_bytes(m, hidden, inter))
+        ws = torch.zeros(ws_bytes, dtype=torch.uint8, device=device)
+        sp = status.data_ptr() + 8
+
+        def ffn(count):
+            st = torch.cuda.current_stream().cuda_stream
+            for i in range(count):
+                wgu, sgu, wd, sd = sets[i % 2]
+                rcs = (lib.bfp8_quant_act_1x128_bf16(x.data_ptr(), m, hidden, hidden, a1.data_ptr(), hidden, s1.data_ptr(), 1, m, 1, None, st),
+                       lib.bfp8_gemm_block128(a1.data_ptr(), hidden, s1.data_ptr(), m, wgu.data_ptr(), hidden, sgu.data_ptr(), None,
+                                              gu.data_ptr(), 1, 2 * inter, m, inter, hidden, ws.data_ptr(), ws_bytes, sp, st),
+                       lib.bfp8_gemm_block128(a1.data_ptr(), hidden, s1.data_ptr(), m, wgu.data_ptr() + inter * hidden, hidden,
+                                              sgu.data_ptr() + 4 * (inter // 128) * (hidden // 128), None,
+                                              gu.data_ptr() + 2 * inter, 1, 2 * inter, m, inter, hidden, ws.data_ptr(), ws_bytes, sp, st),
+                       lib.bfp8_silu_quant_act_1x128_bf16(gu.data_ptr(), m, inter, 2 * inter, a2.data_ptr(), inter, s2.data_ptr(),
+                                                          1, m, 1, None, st),
+                       lib.bfp8_gemm_block128(a2.data_ptr(), inter, s2.data_ptr(), m, wd.data_ptr(), inter, sd.data_ptr(), None,
+                                              y.data_ptr(), 1, hidden, m, hidden, inter, ws.data_ptr(), ws_bytes, sp, st))
+                assert rcs == (0, 0, 0, 0, 0), rcs
+
+        ffn(2)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            ffn(reps)
+        ts = []
+        for _ in range(rounds):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1) / reps)
+        us = statistics.median(ts) * 1e3
+        nbytes = 3 * inter * hidden                                  # weight codes; everything else is below 1 %
+        out["M=%d" % m] = {"us": round(us, 2), "weight_gbs": round(nbytes / us / 1e3, 1), "kernels": 5}
+    assert int(status.cpu()[2]) == 0
+    return out
+
+
 def bench_checkpoint_stream(torch, device, tensors=12, n=8192, k=8192):
     """Load-time pipeline: `tensors` pinned host weights of n x k codes streamed to the GPU and re-encoded.
 
@@ -650,6 +715,10 @@ def main():
             for v in decode.values():
                 v["hbm_frac_of_measured"] = round(v["gbs"] / hbm_gbs, 3)
             line["decode_bucket_k%d_n%d" % (dk, dn)] = decode
+        ffn = bench_decode_ffn(torch, lib, device)
+        for v in ffn.values():
+            v["hbm_frac_of_measured"] = round(v["weight_gbs"] / hbm_gbs, 3)
+        line["decode_ffn_hidden4096_inter14336"] = ffn
         line["checkpoint_stream_h2d_reencode"] = bench_checkpoint_stream(torch, device)
     if gather is not None:
         line["gather"] = gather

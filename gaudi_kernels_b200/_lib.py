@@ -37,6 +37,7 @@ SIGNATURES = {
     "bfp8_gemm_block128_noalloc": (_int, [_ptr, _i64, _ptr, _i64, _ptr, _i64, _ptr, _ptr, _ptr, _int, _i64,
                                           _i64, _i64, _i64, _ptr, _ptr]),
     "bfp8_silu_and_mul_bf16": (_int, [_ptr, _i64, _ptr, _i64, _i64, _i64, _ptr]),
+    "bfp8_silu_quant_act_1x128_bf16": (_int, [_ptr, _i64, _i64, _i64, _ptr, _i64, _ptr, _i64, _i64, _int, _ptr, _ptr]),
     "bfp8_rank_sum": (_int, [_ptr, _ptr, _i64, _int, _int, _ptr]),
     "bfp8_rank_sum_slices": (_int, [_ptr, _ptr, _i64, _int, _int, _ptr, _i64, _ptr]),
     "bfp8_gemm_block128_push": (_int, [_ptr, _i64, _ptr, _i64, _ptr, _i64, _ptr, _ptr, _int, _int,

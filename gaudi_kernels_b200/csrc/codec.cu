@@ -184,12 +184,25 @@ quant_block128_kernel(const float* __restrict__ w, int64_t rows, int64_t cols, i
 constexpr int kActThreads = 256;
 constexpr int kActPer = 2;            // groups per half-warp and iteration
 
-template <bool kVec>
+// silu(g) * u of csrc/tpc/generic_dense/silu_and_mul_bf16.c:4-13, rounded to bf16 as that kernel stores it; the
+// same expression as the GEMM's fused epilogue and the stand-alone kernel, so all three agree bit for bit.
+__device__ __forceinline__ float silu_mul_bf16_rounded(float g, float u) {
+  const float q = __fdividef(g, 1.0f + __expf(-g));
+  return bf16_bits_to_float(float_to_bf16_bits((g <= -88.0f ? 0.0f : q) * u));
+}
+
+// kSilu: x is a gate/up pair [m, 2 k] (gate columns, then up columns, row pitch ldx) and the values quantized are
+// bf16(silu(gate) * up) - gk_silu_and_mul_bf16_v1 followed by the 1x128 quantizer, without the round trip of the
+// intermediate tensor through HBM.
+template <bool kVec, bool kSilu>
 __global__ void __launch_bounds__(kActThreads, 6)
 quant_act_1x128_kernel(const uint16_t* __restrict__ x, int64_t m, int64_t k, int64_t ldx,
                        uint8_t* __restrict__ codes, int64_t ld_codes, float* __restrict__ scales,
                        int64_t ssm, int64_t ssg, int groups, int native_half,
-                       uint32_t* __restrict__ status) {
+                       uint32_t* __restrict__ status, int iters_per_cta) {
+  // launched with programmatic stream serialization: let the next kernel be scheduled, then wait for the previous one
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int sub = threadIdx.x & 15;                            // lane inside the half-warp
   const int hw = threadIdx.x >> 4;                             // half-warp inside the CTA, 0..15
   uint32_t nonfinite = 0;
@@ -207,19 +220,25 @@ quant_act_1x128_kernel(const uint16_t* __restrict__ x, int64_t m, int64_t k, int
     const bool row_ok = row < m;
     const uint16_t* xrow = x + row * ldx;
     uint8_t* crow = codes + row * ld_codes;
-    for (int gi = 0; gi < g_iters; ++gi) {
+    // with few rows the passes over a long row are spread over blockIdx.y, so that a decode-sized call is not
+    // one CTA walking the whole row
+    const int gi_end = min(g_iters, (static_cast<int>(blockIdx.y) + 1) * iters_per_cta);
+    for (int gi = blockIdx.y * iters_per_cta; gi < gi_end; ++gi) {
       bool live[kActPer];
       int g[kActPer];
       int64_t col[kActPer];
-      uint4 raw[kActPer];
+      uint4 raw[kActPer], raw_up[kSilu ? kActPer : 1];
 #pragma unroll
       for (int u = 0; u < kActPer; ++u) {
         g[u] = g_first + (gi * kActPer + u) * g_step;
         live[u] = row_ok && g[u] < groups;
         col[u] = static_cast<int64_t>(g[u]) * 128 + sub * 8;
         raw[u] = make_uint4(0u, 0u, 0u, 0u);
-        if (kVec && live[u] && col[u] < k)                                // k % 8 == 0 on this path
+        if (kSilu) raw_up[u] = make_uint4(0u, 0u, 0u, 0u);
+        if (kVec && live[u] && col[u] < k) {                              // k % 8 == 0 on this path
           raw[u] = __ldcs(reinterpret_cast<const uint4*>(xrow + col[u]));
+          if (kSilu) raw_up[u] = __ldcs(reinterpret_cast<const uint4*>(xrow + k + col[u]));
+        }
       }
 #pragma unroll
       for (int u = 0; u < kActPer; ++u) {
@@ -231,11 +250,22 @@ quant_act_1x128_kernel(const uint16_t* __restrict__ x, int64_t m, int64_t k, int
             f[2 * j] = bf16_lo_to_float(r[j]);
             f[2 * j + 1] = bf16_hi_to_float(r[j]);
           }
+          if (kSilu) {
+            const uint32_t* ru = reinterpret_cast<const uint32_t*>(&raw_up[u]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              f[2 * j] = silu_mul_bf16_rounded(f[2 * j], bf16_lo_to_float(ru[j]));
+              f[2 * j + 1] = silu_mul_bf16_rounded(f[2 * j + 1], bf16_hi_to_float(ru[j]));
+            }
+          }
         } else {
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             f[j] = 0.0f;
-            if (live[u] && col[u] + j < k) f[j] = bf16_bits_to_float(xrow[col[u] + j]);
+            if (live[u] && col[u] + j < k) {
+              f[j] = bf16_bits_to_float(xrow[col[u] + j]);
+              if (kSilu) f[j] = silu_mul_bf16_rounded(f[j], bf16_bits_to_float(xrow[k + col[u] + j]));
+            }
           }
         }
         // NaN-propagating maximum: an inf or NaN anywhere in the group surfaces in amax
@@ -538,16 +568,34 @@ extern "C" int bfp8_quant_act_1x128_bf16(const uint16_t* x, int64_t m, int64_t k
   if (want > 2147483647LL) return BFP8_ERR_SHAPE;
   const int grid = static_cast<int>(want);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (vec)
-    quant_act_1x128_kernel<true><<<grid, kActThreads, 0, st>>>(x, m, k, ldx, codes, ld_codes, scales, scale_stride_m,
-                                                               scale_stride_g, static_cast<int>(groups), native_half,
-                                                               status_dev);
-  else
-    quant_act_1x128_kernel<false><<<grid, kActThreads, 0, st>>>(x, m, k, ldx, codes, ld_codes, scales, scale_stride_m,
-                                                                scale_stride_g, static_cast<int>(groups), native_half,
-                                                                status_dev);
-  BFP8_CUDA_TRY(cudaGetLastError());
-  return BFP8_OK;
+  const int passes = static_cast<int>((groups + 16 * kActPer - 1) / (16 * kActPer));
+  const int split = (want < 2LL * sm_count() && passes <= 65535) ? passes : 1;      // few rows: one pass per CTA
+  return launch_overlapped(vec ? quant_act_1x128_kernel<true, false> : quant_act_1x128_kernel<false, false>,
+                           dim3(grid, split), dim3(kActThreads), 0, st, x, m, k, ldx, codes, ld_codes, scales,
+                           scale_stride_m, scale_stride_g, static_cast<int>(groups), native_half, status_dev,
+                           split > 1 ? 1 : passes);
+}
+
+extern "C" int bfp8_silu_quant_act_1x128_bf16(const uint16_t* gate_up, int64_t m, int64_t inter, int64_t ld_in,
+                                              uint8_t* codes, int64_t ld_codes,
+                                              float* scales, int64_t scale_stride_m, int64_t scale_stride_g,
+                                              int native_half, uint32_t* status_dev, void* stream) {
+  if (!gate_up || !codes || !scales) return BFP8_ERR_NULL;
+  if (m <= 0 || inter <= 0 || ld_in < 2 * inter || ld_codes < inter || scale_stride_m <= 0 || scale_stride_g <= 0)
+    return BFP8_ERR_SHAPE;
+  if (!aligned(gate_up, 2) || !aligned(scales, 4)) return BFP8_ERR_ALIGN;
+  const int64_t groups = (inter + 127) / 128;
+  if (groups > (1 << 24)) return BFP8_ERR_SHAPE;
+  const bool vec = aligned(gate_up, 16) && aligned(codes, 8) && ld_in % 8 == 0 && ld_codes % 8 == 0 && inter % 8 == 0;
+  const int rows_per_cta = groups >= 16 ? 1 : static_cast<int>(16 / groups);
+  const int64_t want = (m + rows_per_cta - 1) / rows_per_cta;
+  if (want > 2147483647LL) return BFP8_ERR_SHAPE;
+  const int passes = static_cast<int>((groups + 16 * kActPer - 1) / (16 * kActPer));
+  const int split = (want < 2LL * sm_count() && passes <= 65535) ? passes : 1;
+  return launch_overlapped(vec ? quant_act_1x128_kernel<true, true> : quant_act_1x128_kernel<false, true>,
+                           dim3(static_cast<unsigned>(want), split), dim3(kActThreads), 0, static_cast<cudaStream_t>(stream),
+                           gate_up, m, inter, ld_in, codes, ld_codes, scales, scale_stride_m, scale_stride_g,
+                           static_cast<int>(groups), native_half, status_dev, split > 1 ? 1 : passes);
 }
 
 extern "C" int bfp8_decode_block128(const uint8_t* codes, int64_t rows, int64_t cols, int64_t ld,

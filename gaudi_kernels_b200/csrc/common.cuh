@@ -39,6 +39,27 @@ inline int ensure_smem_limit(Kernel kernel, int bytes, bool (&done)[64]) {
   return BFP8_OK;
 }
 
+// Launch with the programmatic-stream-serialization attribute: the kernel may be scheduled while the previous
+// kernel of the stream is still finishing and must call ptx::griddep_wait() (or the griddepcontrol.wait
+// instruction) before it touches global memory.  Used for the short kernels of a decode step, where the launch
+// path is a large part of the run time.
+template <typename... KArgs, typename... Args>
+inline int launch_overlapped(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                             Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  BFP8_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...));
+  return BFP8_OK;
+}
+
 // ---- E4M3 byte arithmetic -----------------------------------------------------------------
 
 // Byte-parallel arithmetic on four packed codes, written with plain 32-bit logic (the __v*4 SIMD

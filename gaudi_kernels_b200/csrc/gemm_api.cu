@@ -173,6 +173,9 @@ __device__ __forceinline__ float silu_mul_f32(float g, float u) {
 __global__ void __launch_bounds__(256)
 silu_and_mul_kernel(const uint16_t* __restrict__ gate_up, int64_t ld_in, uint16_t* __restrict__ out, int64_t ld_out,
                     int64_t rows, int64_t inter, int vec_ok) {
+  // launched with programmatic stream serialization (see launch_overlapped)
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   if (vec_ok) {
     const int64_t vecs = inter >> 3, total = rows * vecs;
     for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
@@ -209,10 +212,8 @@ extern "C" int bfp8_silu_and_mul_bf16(const uint16_t* gate_up, int64_t ld_in, ui
   const int vec = aligned(gate_up, 16) && aligned(out, 16) && inter % 8 == 0 && ld_in % 8 == 0 && ld_out % 8 == 0;
   const int64_t work = vec ? rows * (inter / 8) : rows * inter;
   const int64_t want = (work + 255) / 256, cap = static_cast<int64_t>(sm_count()) * 8;
-  silu_and_mul_kernel<<<static_cast<int>(want < cap ? want : cap), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      gate_up, ld_in, out, ld_out, rows, inter, vec);
-  BFP8_CUDA_TRY(cudaGetLastError());
-  return BFP8_OK;
+  return launch_overlapped(silu_and_mul_kernel, dim3(static_cast<unsigned>(want < cap ? want : cap)), dim3(256), 0,
+                           static_cast<cudaStream_t>(stream), gate_up, ld_in, out, ld_out, rows, inter, vec);
 }
 
 // ---- row-parallel GEMM whose epilogue scatters its tiles to the GPUs that reduce them -------------------

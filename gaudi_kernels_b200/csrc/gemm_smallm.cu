@@ -140,6 +140,11 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   __syncthreads();
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = tail->tmem_base;
+  // Everything above touches only this CTA's shared memory and TMEM, so under a programmatic dependent launch it
+  // runs while the previous kernel of the stream is still finishing; from here on global memory is read and
+  // written (activations and workspace may come from that kernel), so every thread waits for it first.
+  ptx::griddep_launch_dependents();
+  ptx::griddep_wait();
 
   if (warp == kEpiWarps) {
     // ------------------------------------------------------------------ TMA producer
@@ -383,8 +388,18 @@ int launch(const CUtensorMap& tmap_w, const CUtensorMap& tmap_a, const Params& p
   static bool done[64] = {};
   const int rc = ensure_smem_limit(gemm_smallm_kernel<MP, false>, smem, done);
   if (rc != BFP8_OK) return rc;
-  gemm_smallm_kernel<MP, false><<<grid, kThreads, smem, st>>>(tmap_w, tmap_a, p);
-  BFP8_CUDA_TRY(cudaGetLastError());
+  // launched so that the set-up of this kernel may overlap the tail of the previous kernel in the stream
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  BFP8_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_smallm_kernel<MP, false>, tmap_w, tmap_a, p));
   return BFP8_OK;
 }
 
@@ -403,13 +418,15 @@ int launch_clustered(const CUtensorMap& tmap_w, const CUtensorMap& tmap_a, const
   cfg.blockDim = dim3(kThreads, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = static_cast<unsigned>(p.cluster);
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = 2;
   // co-residency of all clusters, asked once per device and cluster size (index log2(cluster) - 1)
   static int max_clusters[64][3] = {};
   int dev = 0;

@@ -42,6 +42,13 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
+// Programmatic dependent launch.  A kernel launched with the programmatic-stream-serialization attribute may
+// start while its predecessor in the stream still runs; `griddep_wait` blocks the calling thread until every
+// predecessor grid has completed and its memory is visible (a no-op for an ordinary launch), and
+// `griddep_launch_dependents` lets the successor's CTAs be scheduled once every CTA of this grid has issued it.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // A CTA whose bounded wait expired leaves with copies into its shared memory and MMAs into its TMEM possibly
 // still in flight; nothing tracks them any more.  Before shared memory and TMEM are given up the CTA therefore
 // idles for about 100 us, orders of magnitude longer than any single bulk copy or MMA takes to land.

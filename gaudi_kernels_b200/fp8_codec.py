@@ -144,6 +144,29 @@ def quantize_act_1x128(x, native_half=False, check_finite=False):
     return codes, scales
 
 
+
+def silu_quantize_act_1x128(gate_up, native_half=False):
+    """bf16 [M, 2 * I] (gate columns, then up columns) -> (E4M3 codes [M, I], fp32 scales [M, ceil(I/128)]).
+
+    gk_silu_and_mul_bf16_v1 (csrc/tpc/generic_dense/silu_and_mul_bf16.c:16) and the 1x128 quantizer of
+    block_fp8_oracle.py:25-28 in one kernel: the same codes and scales as
+    quantize_act_1x128(silu_and_mul(gate_up)), without writing and re-reading the [M, I] product.
+    """
+    if (not isinstance(gate_up, torch.Tensor) or gate_up.dtype != torch.bfloat16 or gate_up.ndim != 2
+            or gate_up.shape[1] % 2 or not gate_up.numel() or gate_up.stride(1) != 1 or gate_up.device.type != "cuda"):
+        raise ValueError("expected a nonempty bf16 [M, 2 * I] CUDA tensor with unit column stride")
+    lib = _lib.load()
+    dev = gate_up.device
+    m, inter = gate_up.shape[0], gate_up.shape[1] // 2
+    g = (inter + BLOCK - 1) // BLOCK
+    with torch.cuda.device(dev):
+        codes = torch.empty((m, inter), dtype=torch.uint8, device=dev)
+        scales_gm = torch.empty((g, m), dtype=torch.float32, device=dev)
+        rc = lib.bfp8_silu_quant_act_1x128_bf16(gate_up.data_ptr(), m, inter, gate_up.stride(0), codes.data_ptr(), inter,
+                                                scales_gm.data_ptr(), 1, m, int(bool(native_half)), None, _stream_ptr())
+        _lib.check(rc, "bfp8_silu_quant_act_1x128_bf16")
+    return codes.view(torch.float8_e4m3fn), scales_gm.t()
+
 def quantize_act_token(x, native_half=True, check_finite=False):
     """bf16 [M, K] -> (E4M3 codes [M, K], fp32 scales [M]): one scale per row.
 

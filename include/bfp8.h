@@ -204,6 +204,16 @@ int bfp8_gemm_block128_swiglu(const uint8_t* a_codes, int64_t lda, const float* 
 int bfp8_silu_and_mul_bf16(const uint16_t* gate_up, int64_t ld_in, uint16_t* out, int64_t ld_out,
                            int64_t rows, int64_t inter, void* stream);
 
+/* bfp8_silu_and_mul_bf16 followed by bfp8_quant_act_1x128_bf16 as one kernel: the values quantized are
+ * bf16(silu(gate_up[r, c]) * gate_up[r, inter + c]) (silu_and_mul_bf16.c:16, rounded as that kernel stores them), the
+ * quantization is block_fp8_oracle.py:25-28 (+ :31-34 with native_half) over groups of 128 columns of the [m, inter]
+ * product.  Codes, scales and status exactly as the two calls would give them; the intermediate tensor never reaches
+ * HBM.  This is the activation side of the down projection that follows a gate/up GEMM in the decode bucket. */
+int bfp8_silu_quant_act_1x128_bf16(const uint16_t* gate_up, int64_t m, int64_t inter, int64_t ld_in,
+                                   uint8_t* codes, int64_t ld_codes,
+                                   float* scales, int64_t scale_stride_m, int64_t scale_stride_g,
+                                   int native_half, uint32_t* status_dev, void* stream);
+
 /* Sum of world_size per-rank slices in canonical rank order: dst[i] = ((s0[i] + s1[i]) + s2[i]) + ... in fp32,
  * rounded once (RNE) for bf16 data.  Replaces gk_rank_sum_bf16_v1 / gk_rank_sum_f32_v1
  * (csrc/tpc/generic_dense/rank_sum.c:4-42; glue csrc/host/generic_dense_glue.cpp:569-600): `gathered` holds the

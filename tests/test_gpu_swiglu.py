@@ -148,3 +148,23 @@ def test_standalone_silu_and_mul_matches_restatement(gk, rows, inter):
         w_il, s_il = gk.prepare_weight_swiglu(codes.cuda(), s.cuda(), native_half=True)
         fused = gk.gemm_block_fp8_swiglu(a_codes, a_scales, w_il, s_il, bias=b.cuda())
         assert torch.equal(two_step, fused)
+
+
+@pytest.mark.parametrize("rows,inter", [(1, 14336), (8, 14336), (64, 1024), (5, 200), (3, 130), (300, 4096)])
+@pytest.mark.parametrize("half", [True, False])
+def test_fused_silu_quantizer_equals_the_two_kernels(gk, rows, inter, half):
+    from oracle import block_fp8_ref
+    g = torch.Generator().manual_seed(rows * 3 + inter)
+    x = (torch.randn((rows, 2 * inter), generator=g) * 4).to(torch.bfloat16)
+    x[0, 0] = -120.0                                    # a product that is exactly zero
+    xd = x.cuda()
+    h = gk.silu_and_mul(xd)
+    want_codes, want_scales = gk.quantize_act_1x128(h, native_half=half)
+    codes, scales = gk.silu_quantize_act_1x128(xd, native_half=half)
+    assert torch.equal(codes.view(torch.uint8), want_codes.view(torch.uint8))
+    assert torch.equal(scales, want_scales)
+    # and the pair is the oracle's quantizer applied to the device's bf16 product
+    groups = (inter + 127) // 128
+    ref_values, ref_scales = block_fp8_ref.quantize_rows(h.cpu(), groups, half)      # values of the codes, [M, G, 128]
+    assert torch.equal(codes.cpu().float(), ref_values.reshape(rows, -1)[:, :inter])
+    assert torch.equal(scales.cpu(), ref_scales.reshape(rows, groups))
