@@ -22,7 +22,9 @@ import cases  # noqa: E402
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: python make_golden.py <path to a checkout of tracycam/gaudi-kernels>")
+    ref_root = sys.argv[1]
     sys.path.insert(0, os.path.join(ref_root, "python"))
     from gaudi_kernels.block_fp8_oracle import reference
     from gaudi_kernels.fp8_codec import reencode_e4m3fn_half
