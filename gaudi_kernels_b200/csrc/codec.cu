@@ -177,12 +177,16 @@ quant_block128_kernel(const float* __restrict__ w, int64_t rows, int64_t cols, i
 }
 
 // ---------------------------------------------------------------------------------------------
-// K3  1x128 activation quantizer: a half-warp (16 lanes x 8 bf16 = 16 B each) owns one group.
-//     A CTA of 16 half-warps walks whole rows (several rows at once when a row has fewer than 16
-//     groups), so no index division sits in the loop; each half-warp has two groups in flight.
+// K3  1x128 activation quantizer: a quarter-warp (8 lanes x 16 bf16 = 32 B each) owns one group, so the
+//     group maximum takes three shuffle steps and the scale arithmetic is shared by 16 elements per lane.
+//     A CTA of 32 quarter-warps with two group slots each covers 64 groups per pass: one row when a row has
+//     at least 64 groups, otherwise 64 / groups rows at once; no index division sits in the loop.
 // ---------------------------------------------------------------------------------------------
 constexpr int kActThreads = 256;
-constexpr int kActPer = 2;            // groups per half-warp and iteration
+constexpr int kActLanes = 8;                                   // lanes per group
+constexpr int kActElems = 128 / kActLanes;                     // elements per lane: 16
+constexpr int kActPer = 2;                                     // group slots per quarter-warp and pass
+constexpr int kActSlots = kActThreads / kActLanes * kActPer;   // group slots per CTA and pass: 64
 
 // silu(g) * u of csrc/tpc/generic_dense/silu_and_mul_bf16.c:4-13, rounded to bf16 as that kernel stores it; the
 // same expression as the GEMM's fused epilogue and the stand-alone kernel, so all three agree bit for bit.
@@ -195,7 +199,7 @@ __device__ __forceinline__ float silu_mul_bf16_rounded(float g, float u) {
 // bf16(silu(gate) * up) - gk_silu_and_mul_bf16_v1 followed by the 1x128 quantizer, without the round trip of the
 // intermediate tensor through HBM.
 template <bool kVec, bool kSilu>
-__global__ void __launch_bounds__(kActThreads, 6)
+__global__ void __launch_bounds__(kActThreads, 4)
 quant_act_1x128_kernel(const uint16_t* __restrict__ x, int64_t m, int64_t k, int64_t ldx,
                        uint8_t* __restrict__ codes, int64_t ld_codes, float* __restrict__ scales,
                        int64_t ssm, int64_t ssg, int groups, int native_half,
@@ -203,99 +207,105 @@ quant_act_1x128_kernel(const uint16_t* __restrict__ x, int64_t m, int64_t k, int
   // launched with programmatic stream serialization: let the next kernel be scheduled, then wait for the previous one
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  const int sub = threadIdx.x & 15;                            // lane inside the half-warp
-  const int hw = threadIdx.x >> 4;                             // half-warp inside the CTA, 0..15
+  const int sub = threadIdx.x & (kActLanes - 1);               // lane inside the quarter-warp
+  const int qw = threadIdx.x / kActLanes;                      // quarter-warp inside the CTA, 0..31
   uint32_t nonfinite = 0;
-  int rows_per_cta, row_off, g_first, g_step;
-  if (groups >= 16) {
-    rows_per_cta = 1; row_off = 0; g_first = hw; g_step = 16;
-  } else {
-    rows_per_cta = 16 / groups; row_off = hw / groups; g_first = hw % groups; g_step = 16;   // one group per row
-    if (row_off >= rows_per_cta) g_first = groups;             // spare half-warps stay idle
+  // slot t = qw + 32 u of a pass is (row offset, group) of this quarter-warp's u-th group
+  const bool whole_row = groups >= kActSlots;
+  const int rows_per_cta = whole_row ? 1 : kActSlots / groups;
+  int row_off[kActPer], g_first[kActPer];
+#pragma unroll
+  for (int u = 0; u < kActPer; ++u) {
+    const int t = qw + (kActThreads / kActLanes) * u;
+    row_off[u] = whole_row ? 0 : t / groups;
+    g_first[u] = whole_row ? t : t - row_off[u] * groups;
+    if (row_off[u] >= rows_per_cta) g_first[u] = groups;       // spare slots stay idle
   }
   // warp-uniform trip counts: shuffles below are warp-wide
-  const int g_iters = (groups + 16 * kActPer - 1) / (16 * kActPer);
-  {
-    const int64_t row = static_cast<int64_t>(blockIdx.x) * rows_per_cta + row_off;
-    const bool row_ok = row < m;
-    const uint16_t* xrow = x + row * ldx;
-    uint8_t* crow = codes + row * ld_codes;
-    // with few rows the passes over a long row are spread over blockIdx.y, so that a decode-sized call is not
-    // one CTA walking the whole row
-    const int gi_end = min(g_iters, (static_cast<int>(blockIdx.y) + 1) * iters_per_cta);
-    for (int gi = blockIdx.y * iters_per_cta; gi < gi_end; ++gi) {
-      bool live[kActPer];
-      int g[kActPer];
-      int64_t col[kActPer];
-      uint4 raw[kActPer], raw_up[kSilu ? kActPer : 1];
+  const int g_iters = whole_row ? (groups + kActSlots - 1) / kActSlots : 1;
+  // with few rows the passes over a long row are spread over blockIdx.y, so that a decode-sized call is not
+  // one CTA walking the whole row
+  const int gi_end = min(g_iters, (static_cast<int>(blockIdx.y) + 1) * iters_per_cta);
+  for (int gi = blockIdx.y * iters_per_cta; gi < gi_end; ++gi) {
+    bool live[kActPer];
+    int g[kActPer];
+    int64_t row[kActPer], col[kActPer];
+    uint4 raw[kActPer][2], raw_up[kSilu ? kActPer : 1][2];
 #pragma unroll
-      for (int u = 0; u < kActPer; ++u) {
-        g[u] = g_first + (gi * kActPer + u) * g_step;
-        live[u] = row_ok && g[u] < groups;
-        col[u] = static_cast<int64_t>(g[u]) * 128 + sub * 8;
-        raw[u] = make_uint4(0u, 0u, 0u, 0u);
-        if (kSilu) raw_up[u] = make_uint4(0u, 0u, 0u, 0u);
-        if (kVec && live[u] && col[u] < k) {                              // k % 8 == 0 on this path
-          raw[u] = __ldcs(reinterpret_cast<const uint4*>(xrow + col[u]));
-          if (kSilu) raw_up[u] = __ldcs(reinterpret_cast<const uint4*>(xrow + k + col[u]));
+    for (int u = 0; u < kActPer; ++u) {
+      row[u] = static_cast<int64_t>(blockIdx.x) * rows_per_cta + row_off[u];
+      g[u] = g_first[u] + gi * kActSlots;
+      // gridDim.z == kActPer (few rows): each CTA serves one of the slots, so twice as many CTAs share a row
+      live[u] = row[u] < m && g[u] < groups && (gridDim.z == 1 || static_cast<int>(blockIdx.z) == u);
+      col[u] = static_cast<int64_t>(g[u]) * 128 + sub * kActElems;
+      const uint16_t* xrow = x + row[u] * ldx;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        raw[u][h] = make_uint4(0u, 0u, 0u, 0u);
+        if (kSilu) raw_up[u][h] = make_uint4(0u, 0u, 0u, 0u);
+        if (kVec && live[u] && col[u] + 8 * h < k) {                      // k % 8 == 0 on this path
+          raw[u][h] = __ldcs(reinterpret_cast<const uint4*>(xrow + col[u] + 8 * h));
+          if (kSilu) raw_up[u][h] = __ldcs(reinterpret_cast<const uint4*>(xrow + k + col[u] + 8 * h));
         }
       }
+    }
 #pragma unroll
-      for (int u = 0; u < kActPer; ++u) {
-        float f[8];
-        if (kVec) {
-          const uint32_t* r = reinterpret_cast<const uint32_t*>(&raw[u]);
+    for (int u = 0; u < kActPer; ++u) {
+      const uint16_t* xrow = x + row[u] * ldx;
+      float f[kActElems];
+      if (kVec) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const uint32_t* r = reinterpret_cast<const uint32_t*>(&raw[u][h]);
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            f[2 * j] = bf16_lo_to_float(r[j]);
-            f[2 * j + 1] = bf16_hi_to_float(r[j]);
+            f[8 * h + 2 * j] = bf16_lo_to_float(r[j]);
+            f[8 * h + 2 * j + 1] = bf16_hi_to_float(r[j]);
           }
           if (kSilu) {
-            const uint32_t* ru = reinterpret_cast<const uint32_t*>(&raw_up[u]);
+            const uint32_t* ru = reinterpret_cast<const uint32_t*>(&raw_up[u][h]);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-              f[2 * j] = silu_mul_bf16_rounded(f[2 * j], bf16_lo_to_float(ru[j]));
-              f[2 * j + 1] = silu_mul_bf16_rounded(f[2 * j + 1], bf16_hi_to_float(ru[j]));
-            }
-          }
-        } else {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            f[j] = 0.0f;
-            if (live[u] && col[u] + j < k) {
-              f[j] = bf16_bits_to_float(xrow[col[u] + j]);
-              if (kSilu) f[j] = silu_mul_bf16_rounded(f[j], bf16_bits_to_float(xrow[k + col[u] + j]));
+              f[8 * h + 2 * j] = silu_mul_bf16_rounded(f[8 * h + 2 * j], bf16_lo_to_float(ru[j]));
+              f[8 * h + 2 * j + 1] = silu_mul_bf16_rounded(f[8 * h + 2 * j + 1], bf16_hi_to_float(ru[j]));
             }
           }
         }
-        // NaN-propagating maximum: an inf or NaN anywhere in the group surfaces in amax
-        float amax = 0.0f;
+      } else {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) amax = max_abs_nan(amax, f[j]);
-#pragma unroll
-        for (int o = 8; o > 0; o >>= 1) amax = max_abs_nan(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-        nonfinite |= !(amax < __int_as_float(0x7f800000));
-        const float s = scale_from_amax(amax);
-        const float rcp = __frcp_rn(s);
-        uint32_t q0, q1;
-        if (native_half) {
-          q0 = quant_half_e4m3x4(f[0], f[1], f[2], f[3], s, rcp);
-          q1 = quant_half_e4m3x4(f[4], f[5], f[6], f[7], s, rcp);
-        } else {
-          q0 = quant_e4m3x4(f[0], f[1], f[2], f[3], s, rcp);
-          q1 = quant_e4m3x4(f[4], f[5], f[6], f[7], s, rcp);
-        }
-        if (live[u]) {
-          uint8_t* p = crow + col[u];
-          if (kVec) {
-            if (col[u] < k) __stcs(reinterpret_cast<uint2*>(p), make_uint2(q0, q1));
-          } else {
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-              if (col[u] + j < k) p[j] = static_cast<uint8_t>((j < 4 ? q0 : q1) >> (8 * (j & 3)));
+        for (int j = 0; j < kActElems; ++j) {
+          f[j] = 0.0f;
+          if (live[u] && col[u] + j < k) {
+            f[j] = bf16_bits_to_float(xrow[col[u] + j]);
+            if (kSilu) f[j] = silu_mul_bf16_rounded(f[j], bf16_bits_to_float(xrow[k + col[u] + j]));
           }
-          if (sub == 0) scales[row * ssm + g[u] * ssg] = native_half ? __fmul_rn(s, 2.0f) : s;
         }
+      }
+      // NaN-propagating maximum: an inf or NaN anywhere in the group surfaces in amax
+      float amax = 0.0f;
+#pragma unroll
+      for (int j = 0; j < kActElems; ++j) amax = max_abs_nan(amax, f[j]);
+#pragma unroll
+      for (int o = kActLanes / 2; o > 0; o >>= 1) amax = max_abs_nan(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+      nonfinite |= !(amax < __int_as_float(0x7f800000));
+      const float s = scale_from_amax(amax);
+      const float rcp = __frcp_rn(s);
+      uint32_t q[4];
+#pragma unroll
+      for (int w = 0; w < 4; ++w)
+        q[w] = native_half ? quant_half_e4m3x4(f[4 * w], f[4 * w + 1], f[4 * w + 2], f[4 * w + 3], s, rcp)
+                           : quant_e4m3x4(f[4 * w], f[4 * w + 1], f[4 * w + 2], f[4 * w + 3], s, rcp);
+      if (live[u]) {
+        uint8_t* p = codes + row[u] * ld_codes + col[u];
+        if (kVec) {
+          if (col[u] < k) __stcs(reinterpret_cast<uint2*>(p), make_uint2(q[0], q[1]));
+          if (col[u] + 8 < k) __stcs(reinterpret_cast<uint2*>(p + 8), make_uint2(q[2], q[3]));
+        } else {
+#pragma unroll
+          for (int j = 0; j < kActElems; ++j)
+            if (col[u] + j < k) p[j] = static_cast<uint8_t>(q[j >> 2] >> (8 * (j & 3)));
+        }
+        if (sub == 0) scales[row[u] * ssm + g[u] * ssg] = native_half ? __fmul_rn(s, 2.0f) : s;
       }
     }
   }
@@ -563,15 +573,16 @@ extern "C" int bfp8_quant_act_1x128_bf16(const uint16_t* x, int64_t m, int64_t k
   const int64_t groups = (k + 127) / 128;
   if (groups > (1 << 24)) return BFP8_ERR_SHAPE;
   const bool vec = aligned(x, 16) && aligned(codes, 8) && ldx % 8 == 0 && ld_codes % 8 == 0 && k % 8 == 0;
-  const int rows_per_cta = groups >= 16 ? 1 : static_cast<int>(16 / groups);
-  const int64_t want = (m + rows_per_cta - 1) / rows_per_cta;           // one CTA per row (or per 16 / groups rows)
+  const int rows_per_cta = groups >= kActSlots ? 1 : static_cast<int>(kActSlots / groups);
+  const int64_t want = (m + rows_per_cta - 1) / rows_per_cta;           // one CTA per row (or per 64 / groups rows)
   if (want > 2147483647LL) return BFP8_ERR_SHAPE;
   const int grid = static_cast<int>(want);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int passes = static_cast<int>((groups + 16 * kActPer - 1) / (16 * kActPer));
+  const int passes = static_cast<int>((groups + kActSlots - 1) / kActSlots);
   const int split = (want < 2LL * sm_count() && passes <= 65535) ? passes : 1;      // few rows: one pass per CTA
   return launch_overlapped(vec ? quant_act_1x128_kernel<true, false> : quant_act_1x128_kernel<false, false>,
-                           dim3(grid, split), dim3(kActThreads), 0, st, x, m, k, ldx, codes, ld_codes, scales,
+                           dim3(grid, split, want < 2LL * sm_count() ? kActPer : 1), dim3(kActThreads), 0, st, x, m, k, ldx,
+                           codes, ld_codes, scales,
                            scale_stride_m, scale_stride_g, static_cast<int>(groups), native_half, status_dev,
                            split > 1 ? 1 : passes);
 }
@@ -587,13 +598,14 @@ extern "C" int bfp8_silu_quant_act_1x128_bf16(const uint16_t* gate_up, int64_t m
   const int64_t groups = (inter + 127) / 128;
   if (groups > (1 << 24)) return BFP8_ERR_SHAPE;
   const bool vec = aligned(gate_up, 16) && aligned(codes, 8) && ld_in % 8 == 0 && ld_codes % 8 == 0 && inter % 8 == 0;
-  const int rows_per_cta = groups >= 16 ? 1 : static_cast<int>(16 / groups);
+  const int rows_per_cta = groups >= kActSlots ? 1 : static_cast<int>(kActSlots / groups);
   const int64_t want = (m + rows_per_cta - 1) / rows_per_cta;
   if (want > 2147483647LL) return BFP8_ERR_SHAPE;
-  const int passes = static_cast<int>((groups + 16 * kActPer - 1) / (16 * kActPer));
+  const int passes = static_cast<int>((groups + kActSlots - 1) / kActSlots);
   const int split = (want < 2LL * sm_count() && passes <= 65535) ? passes : 1;
   return launch_overlapped(vec ? quant_act_1x128_kernel<true, true> : quant_act_1x128_kernel<false, true>,
-                           dim3(static_cast<unsigned>(want), split), dim3(kActThreads), 0, static_cast<cudaStream_t>(stream),
+                           dim3(static_cast<unsigned>(want), split, want < 2LL * sm_count() ? kActPer : 1), dim3(kActThreads), 0,
+                           static_cast<cudaStream_t>(stream),
                            gate_up, m, inter, ld_in, codes, ld_codes, scales, scale_stride_m, scale_stride_g,
                            static_cast<int>(groups), native_half, status_dev, split > 1 ? 1 : passes);
 }
