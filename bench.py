@@ -461,24 +461,36 @@ def run_reference(args, workload, m, k, n, world, rank):
     import numpy as np
     # launchers such as torch.distributed.run pin OMP_NUM_THREADS to 1; the CPU arm uses every host core
     torch.set_num_threads(max(1, os.cpu_count() or 1))
-    rows = max(1, args.cpu_rows)
     rng = np.random.default_rng(0)
-    x = torch.from_numpy(rng.standard_normal((rows, k), dtype=np.float32)).to(torch.bfloat16)
     wf = torch.randn((n, k), generator=torch.Generator().manual_seed(1)) * 0.02
     codes, scales = fp8_codec_ref.quantize_block128(wf.numpy())
     del wf
     w = torch.from_numpy(codes).view(torch.float8_e4m3fn)
     s = torch.from_numpy(scales)
+    x_all = torch.from_numpy(rng.standard_normal((m, k), dtype=np.float32)).to(torch.bfloat16)
+
+    def one(rows):
+        t0 = time.perf_counter()
+        block_fp8_ref.reference(x_all[:rows], w, s, native_half=True)
+        return time.perf_counter() - t0
+
+    # Size the per-step sample so that the whole run takes about two minutes: a call costs a fixed part (weight
+    # preparation) plus a per-row part, both measured here on two small samples.
+    r_small, r_big = max(1, args.cpu_rows), min(m, 8 * max(1, args.cpu_rows))
+    t_small, t_big = one(r_small), one(r_big)
+    per_row = max((t_big - t_small) / max(r_big - r_small, 1), 1e-9)
+    fixed = max(t_small - per_row * r_small, 0.0)
+    warmup = min(args.warmup, 1)        # CPU timing needs no long warm-up; keeps the arm within a few minutes
+    budget = 120.0 / max(args.steps + warmup, 1)
+    rows = int(min(m, max(r_small, (budget - fixed) / per_row)))
+    rows = max(r_small, rows // 32 * 32 if rows >= 32 else rows)
     flops = 2.0 * rows * k * n
     times = []
-    warmup = min(args.warmup, 2)        # CPU timing needs no long warm-up; keeps the arm within a few minutes
     for i in range(warmup + args.steps):
-        t0 = time.perf_counter()
-        block_fp8_ref.reference(x, w, s, native_half=True)
-        dt = time.perf_counter() - t0
+        dt = one(rows)
         if i >= warmup:
             times.append(dt)
-        if sum(times) > 90.0:           # bounded whatever the host is
+        if sum(times) > 150.0:          # bounded whatever the host is
             break
     per_step = sum(times) / len(times)
     value = flops / per_step / 1e12
