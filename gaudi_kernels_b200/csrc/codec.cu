@@ -452,6 +452,7 @@ quant_act_token_warp_kernel(const uint16_t* __restrict__ x, int64_t m, int64_t k
 //     16-byte (fp32) or 8-byte (bf16) store, so both sides of every warp access are contiguous.
 // ---------------------------------------------------------------------------------------------
 constexpr int kDecodeThreads = 256;
+constexpr int kDecodePer = 4;          // quads per thread
 
 template <bool kVec, bool kBf16, typename Idx>
 __global__ void __launch_bounds__(kDecodeThreads)
@@ -459,42 +460,59 @@ decode_block128_kernel(const uint8_t* __restrict__ codes, int64_t rows, int64_t 
                        const float* __restrict__ scales, int col_blocks, void* __restrict__ out,
                        int64_t ld_out) {
   // Idx is 32-bit whenever rows * ceil(cols/4) fits, which keeps the row/column split cheap.
+  // A thread decodes kDecodePer quads, one grid-stride apart, and issues all of their loads (codes and scale)
+  // before the first use: with one quad per thread the kernel sat on the latency of its two 4-byte loads.
   const Idx quads_per_row = static_cast<Idx>((cols + 3) >> 2);
   const Idx total = static_cast<Idx>(rows) * quads_per_row;
-  const Idx i = static_cast<Idx>(blockIdx.x) * blockDim.x + threadIdx.x;      // one quad per thread
-  if (i < total) {
-    const int64_t r = i / quads_per_row, c = static_cast<int64_t>(i % quads_per_row) << 2;
-    const float s = __ldg(scales + (r >> 7) * col_blocks + (c >> 7));
-    const uint8_t* p = codes + r * ld + c;
-    uint32_t q = 0;
-    if (kVec) {
-      q = __ldcs(reinterpret_cast<const uint32_t*>(p));
-    } else {
+  const Idx stride = static_cast<Idx>(gridDim.x) * blockDim.x;
+  const Idx first = static_cast<Idx>(blockIdx.x) * blockDim.x + threadIdx.x;
+  int64_t r[kDecodePer], c[kDecodePer];
+  uint32_t q[kDecodePer];
+  float s[kDecodePer];
+  bool on[kDecodePer];
 #pragma unroll
-      for (int j = 0; j < 4; ++j)
-        if (c + j < cols) q |= static_cast<uint32_t>(p[j]) << (8 * j);
+  for (int u = 0; u < kDecodePer; ++u) {
+    const Idx i = first + static_cast<Idx>(u) * stride;
+    on[u] = i < total;
+    r[u] = 0; c[u] = 0; q[u] = 0; s[u] = 0.0f;
+    if (on[u]) {
+      r[u] = i / quads_per_row;
+      c[u] = static_cast<int64_t>(i % quads_per_row) << 2;
+      s[u] = __ldg(scales + (r[u] >> 7) * col_blocks + (c[u] >> 7));
+      const uint8_t* p = codes + r[u] * ld + c[u];
+      if (kVec) {
+        q[u] = __ldcs(reinterpret_cast<const uint32_t*>(p));
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (c[u] + j < cols) q[u] |= static_cast<uint32_t>(p[j]) << (8 * j);
+      }
     }
-    const float2 lo = e4m3x2_to_float2(q & 0xffffu), hi = e4m3x2_to_float2(q >> 16);
-    const float v0 = __fmul_rn(lo.x, s), v1 = __fmul_rn(lo.y, s), v2 = __fmul_rn(hi.x, s), v3 = __fmul_rn(hi.y, s);
+  }
+#pragma unroll
+  for (int u = 0; u < kDecodePer; ++u) {
+    if (!on[u]) continue;
+    const float2 lo = e4m3x2_to_float2(q[u] & 0xffffu), hi = e4m3x2_to_float2(q[u] >> 16);
+    const float v0 = __fmul_rn(lo.x, s[u]), v1 = __fmul_rn(lo.y, s[u]), v2 = __fmul_rn(hi.x, s[u]), v3 = __fmul_rn(hi.y, s[u]);
     if (kBf16) {
-      uint16_t* o = reinterpret_cast<uint16_t*>(out) + r * ld_out + c;
+      uint16_t* o = reinterpret_cast<uint16_t*>(out) + r[u] * ld_out + c[u];
       if (kVec) {
         __stcs(reinterpret_cast<uint2*>(o), make_uint2(pack_bf16x2(v0, v1), pack_bf16x2(v2, v3)));
       } else {
         const float v[4] = {v0, v1, v2, v3};
 #pragma unroll
         for (int j = 0; j < 4; ++j)
-          if (c + j < cols) o[j] = static_cast<uint16_t>(float_to_bf16_bits(v[j]));
+          if (c[u] + j < cols) o[j] = static_cast<uint16_t>(float_to_bf16_bits(v[j]));
       }
     } else {
-      float* o = reinterpret_cast<float*>(out) + r * ld_out + c;
+      float* o = reinterpret_cast<float*>(out) + r[u] * ld_out + c[u];
       if (kVec) {
         __stcs(reinterpret_cast<float4*>(o), make_float4(v0, v1, v2, v3));
       } else {
         const float v[4] = {v0, v1, v2, v3};
 #pragma unroll
         for (int j = 0; j < 4; ++j)
-          if (c + j < cols) o[j] = v[j];
+          if (c[u] + j < cols) o[j] = v[j];
       }
     }
   }
@@ -623,7 +641,7 @@ extern "C" int bfp8_decode_block128(const uint8_t* codes, int64_t rows, int64_t 
                    aligned(out, bf16 ? 8 : 16);
   const int64_t quads = rows * ((cols + 3) / 4);
   if ((quads + kDecodeThreads - 1) / kDecodeThreads > 2147483647LL) return BFP8_ERR_SHAPE;
-  const int grid = static_cast<int>((quads + kDecodeThreads - 1) / kDecodeThreads);
+  const int grid = static_cast<int>((quads + kDecodeThreads * kDecodePer - 1) / (kDecodeThreads * kDecodePer));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const bool small = rows * ((cols + 3) / 4) < (1LL << 30);
 #define BFP8_LAUNCH_DECODE(V, B)                                                                            \
