@@ -447,6 +447,70 @@ quant_act_token_warp_kernel(const uint16_t* __restrict__ x, int64_t m, int64_t k
   }
 }
 
+// Rows of up to 4096 columns, second form: 128 threads per row (two rows per CTA), four 16-byte loads per thread,
+// the row maximum combined through shared memory and a 128-thread named barrier.  Fewer registers than the
+// warp-per-row form, so four times as many warps are resident and hide the load latency.
+constexpr int kTokHalfThreads = 128;
+constexpr int kTokHalfVecs = 4;
+constexpr int kTokHalfMaxK = kTokHalfVecs * kTokHalfThreads * 8;     // 4096
+
+__global__ void __launch_bounds__(2 * kTokHalfThreads, 4)
+quant_act_token_half_kernel(const uint16_t* __restrict__ x, int64_t m, int64_t k, int64_t ldx,
+                            uint8_t* __restrict__ codes, int64_t ld_codes, float* __restrict__ scales,
+                            int native_half, uint32_t* __restrict__ status) {
+  __shared__ float warp_max[2][kTokHalfThreads / 32];
+  const int half = threadIdx.x / kTokHalfThreads;                  // which of the CTA's two rows
+  const int t = threadIdx.x - half * kTokHalfThreads;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * 2 + half;
+  const bool row_ok = row < m;
+  const uint4* xrow = reinterpret_cast<const uint4*>(x + (row_ok ? row : 0) * ldx);
+  uint2* crow = reinterpret_cast<uint2*>(codes + (row_ok ? row : 0) * ld_codes);
+  const int nvec = row_ok ? static_cast<int>(k >> 3) : 0;
+  uint4 raw[kTokHalfVecs];
+#pragma unroll
+  for (int u = 0; u < kTokHalfVecs; ++u) {
+    const int i = u * kTokHalfThreads + t;
+    raw[u] = make_uint4(0u, 0u, 0u, 0u);
+    if (i < nvec) raw[u] = __ldcs(xrow + i);
+  }
+  float amax = 0.0f;
+#pragma unroll
+  for (int u = 0; u < kTokHalfVecs; ++u) {
+    const uint32_t* r = reinterpret_cast<const uint32_t*>(&raw[u]);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) amax = max_abs_nan(max_abs_nan(amax, bf16_lo_to_float(r[j])), bf16_hi_to_float(r[j]));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = max_abs_nan(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if ((t & 31) == 0) warp_max[half][t >> 5] = amax;
+  asm volatile("bar.sync %0, %1;" ::"r"(1 + half), "r"(kTokHalfThreads) : "memory");
+  amax = warp_max[half][0];
+#pragma unroll
+  for (int i = 1; i < kTokHalfThreads / 32; ++i) amax = max_abs_nan(amax, warp_max[half][i]);
+  if (row_ok && !(amax < __int_as_float(0x7f800000)) && t == 0 && status != nullptr)
+    atomicOr(status, BFP8_STATUS_NONFINITE_INPUT);
+  const float s = __fdiv_rn(amax == 0.0f ? 1.0f : amax, 448.0f);
+  const float rcp = __frcp_rn(s);
+  if (row_ok && t == 0) scales[row] = native_half ? __fmul_rn(s, 2.0f) : s;
+#pragma unroll
+  for (int u = 0; u < kTokHalfVecs; ++u) {
+    const int i = u * kTokHalfThreads + t;
+    const uint32_t* r = reinterpret_cast<const uint32_t*>(&raw[u]);
+    float f[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { f[2 * j] = bf16_lo_to_float(r[j]); f[2 * j + 1] = bf16_hi_to_float(r[j]); }
+    uint2 q;
+    if (native_half) {
+      q.x = quant_half_e4m3x4(f[0], f[1], f[2], f[3], s, rcp);
+      q.y = quant_half_e4m3x4(f[4], f[5], f[6], f[7], s, rcp);
+    } else {
+      q.x = quant_e4m3x4(f[0], f[1], f[2], f[3], s, rcp);
+      q.y = quant_e4m3x4(f[4], f[5], f[6], f[7], s, rcp);
+    }
+    if (i < nvec) __stcs(crow + i, q);
+  }
+}
+
 // ---------------------------------------------------------------------------------------------
 // K4  decode: value(code) * block scale.  A thread turns 4 codes (one 32-bit load) into one
 //     16-byte (fp32) or 8-byte (bf16) store, so both sides of every warp access are contiguous.
@@ -667,7 +731,11 @@ extern "C" int bfp8_quant_act_token_bf16(const uint16_t* x, int64_t m, int64_t k
   if (m <= 0 || k <= 0 || ldx < k || ld_codes < k || m > 2147483647LL) return BFP8_ERR_SHAPE;
   if (!aligned(x, 2) || !aligned(scales, 4)) return BFP8_ERR_ALIGN;
   const int vec = aligned(x, 16) && aligned(codes, 8) && ldx % 8 == 0 && ld_codes % 8 == 0 && k % 8 == 0;
-  if (vec && k <= kTokWarpMaxK) {
+  if (vec && k <= kTokHalfMaxK && m >= 4LL * sm_count()) {
+    quant_act_token_half_kernel<<<static_cast<int>((m + 1) / 2), 2 * kTokHalfThreads, 0,
+                                  static_cast<cudaStream_t>(stream)>>>(x, m, k, ldx, codes, ld_codes, scales,
+                                                                       native_half, status_dev);
+  } else if (vec && k <= kTokWarpMaxK) {
     const int rows_per_cta = kTokWarpThreads / 32;
     quant_act_token_warp_kernel<<<static_cast<int>((m + rows_per_cta - 1) / rows_per_cta), kTokWarpThreads, 0,
                                   static_cast<cudaStream_t>(stream)>>>(x, m, k, ldx, codes, ld_codes, scales,
