@@ -35,8 +35,8 @@ __device__ __forceinline__ void reencode_vec(uint4& v, uint32_t& inexact, uint32
 }
 
 __global__ void __launch_bounds__(kReencodeThreads)
-reencode_half_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, int64_t n, int vec_ok,
-                     const float* __restrict__ scales_in, float* __restrict__ scales_out, int64_t n_scales,
+reencode_half_kernel(const uint8_t* in, uint8_t* out, int64_t n, int vec_ok,          // in == out is allowed
+                     const float* scales_in, float* scales_out, int64_t n_scales,
                      unsigned long long* __restrict__ rounded, uint32_t* __restrict__ status) {
   __shared__ uint32_t cta_inexact, cta_bad;
   if (threadIdx.x == 0) { cta_inexact = 0; cta_bad = 0; }

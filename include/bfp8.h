@@ -10,8 +10,10 @@
  *   - Conditions only the device can see are OR-ed into a caller-owned 32-bit status word
  *     (BFP8_STATUS_* bits).  The caller zeroes it before the first call and reads it after
  *     synchronising; several calls may share one word.
- *   - The library keeps no mutable global state except a per-process cache of driver entry
- *     points; calls are re-entrant and may be issued from several host threads on different streams.
+ *   - The library's only mutable global state is caches of facts about the device (driver entry points, SM
+ *     count, per-kernel shared-memory and cluster limits) and the fixed scratch of
+ *     bfp8_gemm_block128_noalloc; calls are re-entrant and may be issued from several host threads on
+ *     different streams (that one entry point excepted, see there).
  *
  * These conventions mirror the reference glue's: integer status codes instead of exceptions, caller-owned
  * buffers, and a size query before any call that needs scratch (two-phase protocol of

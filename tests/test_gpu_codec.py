@@ -184,3 +184,28 @@ def test_decode_all_codes(gk):
     want = ref.e4m3_values()
     ok = np.isfinite(want)
     assert np.array_equal(got[ok], want[ok]) and np.isnan(got[~ok]).all()
+
+
+@pytest.mark.parametrize("n", [1, 15, 4096 + 3, (1 << 20) + 17])
+def test_reencode_in_place_through_the_c_abi(gk, n):
+    """codes_out == codes_in and scales_out == scales_in, which the header allows: same bytes as out of place."""
+    from gaudi_kernels_b200 import _lib
+    lib = _lib.load()
+    rng = np.random.default_rng(n)
+    codes = rng.integers(0, 256, size=n, dtype=np.uint8)
+    codes[(codes & 0x7f) == 0x7f] ^= 0x01
+    scales = rng.random(7, dtype=np.float32)
+    want_codes, want_scales, want_rounded = ref.reencode_e4m3fn_half(codes, scales)
+    holder = torch.zeros(n + 32, dtype=torch.uint8, device="cuda")
+    for offset in (0, 5):                                            # aligned and unaligned start
+        buf = holder[offset:offset + n]
+        buf.copy_(torch.from_numpy(codes))
+        sc = torch.from_numpy(scales).cuda()
+        st = torch.zeros(4, dtype=torch.int32, device="cuda")
+        rc = lib.bfp8_reencode_half(buf.data_ptr(), buf.data_ptr(), n, sc.data_ptr(), sc.data_ptr(), sc.numel(),
+                                    st.data_ptr(), st.data_ptr() + 8, torch.cuda.current_stream().cuda_stream)
+        assert rc == 0
+        host = st.cpu()
+        assert int(host[2]) == 0 and (int(host[1]) << 32 | (int(host[0]) & 0xFFFFFFFF)) == want_rounded
+        assert np.array_equal(buf.cpu().numpy(), want_codes)
+        assert np.array_equal(sc.cpu().numpy(), want_scales)
