@@ -63,6 +63,8 @@ def parse_args():
     ap.add_argument("--e2e-steps", type=int, default=None, help="steps of the host-buffer leg (default: min(steps, 5))")
     ap.add_argument("--cpu-rows", type=int, default=32, help="activation rows of the CPU-baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-budget-s", type=float, default=120.0,
+                    help="host time the --impl reference run aims to take in all (sizes its per-step sample)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the codec, decode-bucket and checkpoint-stream figures of the N=1 line (short profiler runs)")
@@ -481,7 +483,7 @@ def run_reference(args, workload, m, k, n, world, rank):
     per_row = max((t_big - t_small) / max(r_big - r_small, 1), 1e-9)
     fixed = max(t_small - per_row * r_small, 0.0)
     warmup = min(args.warmup, 1)        # CPU timing needs no long warm-up; keeps the arm within a few minutes
-    budget = 120.0 / max(args.steps + warmup, 1)
+    budget = args.cpu_budget_s / max(args.steps + warmup, 1)
     rows = int(min(m, max(r_small, (budget - fixed) / per_row)))
     rows = max(r_small, rows // 32 * 32 if rows >= 32 else rows)
     flops = 2.0 * rows * k * n

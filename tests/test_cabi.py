@@ -122,3 +122,21 @@ def test_rank_sum_restatement_known_answers():
     assert float(rank_sum_ref.rank_sum(y, 3)[0]) == 1.0 + 2.0 ** -7
     two = torch.tensor([1.5, -0.25, 2.0, 4.0], dtype=torch.float32)
     assert rank_sum_ref.rank_sum(two, 2).tolist() == [3.5, 3.75]
+
+
+def test_bench_reference_arm_prints_the_contract_line():
+    """`bench.py --impl reference` runs on host cores only and prints one JSON line with the agreed keys."""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference", "--steps", "2", "--warmup", "0",
+                          "--cpu-rows", "2", "--cpu-budget-s", "1"], capture_output=True, text=True, timeout=300, cwd=root)
+    assert out.returncode == 0, out.stderr[-500:]
+    line = json.loads(out.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and line["metric"] == "block_fp8_gemm_tflops" and line["unit"] == "TFLOP/s"
+    assert line["steps"] == 2 and line["n_gpus"] == 1 and line["higher_is_better"] is True and line["value"] > 0
+    assert line["cpu_baseline"]["kind"] == "port" and line["cpu_baseline"]["cores"] >= 1
+    assert line["e2e"] == {"value": line["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+    assert line["gpu_launches"] == 0 and "prefill_up" in line["config"]["workload"]
