@@ -3,11 +3,17 @@
 Inputs come from numpy's PCG64 generator (bit-reproducible across machines), not
 from any dataset.  Shapes follow the block-FP8 path's configurations: the
 M=256, K=N=1024 CPU case, a biased ragged-M case, a case whose K and N are not
-multiples of 128, and two cases that re-state the input recipe of the reference's
+multiples of 128, and cases that re-state the input recipe of the reference's
 simulator test (tests/fp8_hybrid_tpcsim_test.cpp:187-231 of tracycam/gaudi-kernels:
 one all-zero row, one all-zero group, 12x / 1.5x envelopes, structured weight
 codes 8..125, the (0.5 + 0.25*((5nb+3g)%11))*1e-3 scale grid, and the
-1e-15 / 1e-12 "tiny" envelopes).
+1e-15 / 1e-12 "tiny" envelopes) at that test's five shapes (:388-392): (37, 256, 384)
+with bias, (4, 128, 256) tiny, and the long-K ones (4, 256, 7168), a 28-group case
+(the reference runs K=7168 a second time in chunks of 28 groups; a contraction that
+is not chunked has no such mode, so the case is K = 28 groups), and (2, 128, 22016).
+The long-K cases also follow the test's sign rule for odd groups (:213-218): the
+weight sign follows whether row 0's activations of the two neighbouring groups agree
+in sign, which makes consecutive K blocks add up instead of cancelling.
 """
 
 import hashlib
@@ -54,7 +60,7 @@ def _gaussian_case(seed, m, k, n, with_bias, store_inputs):
                 store_inputs=store_inputs)
 
 
-def _simulator_style_case(seed, m, n, k, with_bias, tiny):
+def _simulator_style_case(seed, m, n, k, with_bias, tiny, correlated_signs=False, store_inputs=True):
     rng = np.random.default_rng(seed)
     groups, blocks = k // 128, n // 128
     x = np.zeros((m, k), dtype=np.float32)
@@ -73,7 +79,16 @@ def _simulator_style_case(seed, m, n, k, with_bias, tiny):
     g = np.arange(groups)[None, :, None]
     i = np.arange(128)[None, None, :]
     codes = ((col * 17 + g * 31 + i * 7) % 118 + 8).astype(np.uint8)
-    sign = ((col * 3 + g * 5 + i) & 1).astype(np.uint8)
+    sign = np.broadcast_to(((col * 3 + g * 5 + i) & 1).astype(np.uint8), (n, groups, 128)).copy()
+    if correlated_signs:
+        # odd groups, lanes not divisible by 5: sign set where row 0's bf16 activations at (g - 1, i) and (g, i)
+        # have the same sign (zero counts as non-negative)
+        x0 = bf16_bits_to_f32(to_bf16_bits(x[0])).reshape(groups, 128)
+        neg = x0 < 0
+        same = np.zeros((groups, 128), dtype=np.uint8)
+        same[1:] = (neg[1:] == neg[:-1]).astype(np.uint8)
+        rule = ((np.arange(groups)[:, None] & 1) == 1) & ((np.arange(128)[None, :] % 5) != 0)
+        sign = np.where(rule[None], same[None], sign).astype(np.uint8)
     codes = (codes | (sign << 7)).reshape(n, k)
     nb = np.arange(blocks)[:, None]
     gg = np.arange(groups)[None, :]
@@ -83,7 +98,7 @@ def _simulator_style_case(seed, m, n, k, with_bias, tiny):
         c = np.arange(n)
         bias = (np.where(c & 1, -0.125, 0.125) + c * 1e-4).astype(np.float32)
     return dict(x_bf16_bits=to_bf16_bits(x), w_codes=np.ascontiguousarray(codes),
-                w_scales=np.ascontiguousarray(scales), bias=bias, store_inputs=True)
+                w_scales=np.ascontiguousarray(scales), bias=bias, store_inputs=store_inputs)
 
 
 def gemm_cases():
@@ -93,6 +108,9 @@ def gemm_cases():
         "ragged": _gaussian_case(2, 3, 208, 136, True, True),
         "sim_edges": _simulator_style_case(3, 37, 256, 384, True, False),
         "sim_tiny": _simulator_style_case(4, 4, 128, 256, False, True),
+        "sim_k7168": _simulator_style_case(5, 4, 256, 7168, False, False, True, False),
+        "sim_k3584": _simulator_style_case(6, 4, 256, 3584, False, False, True, False),
+        "sim_k22016": _simulator_style_case(7, 2, 128, 22016, False, False, True, False),
     }
 
 

@@ -258,3 +258,95 @@ def test_gemm_prefill_shape_row_sample(gk):
     # linearity in the weight scales (size-independent property): doubling every scale doubles the output exactly
     out_2x = gk.gemm_block_fp8(a_codes, a_scales, wc, ws * 2, out_dtype=torch.float32)
     assert torch.equal(out_2x, out32 * 2)
+
+
+LONG_K_CASES = ("sim_k7168", "sim_k3584", "sim_k22016")
+
+
+@pytest.mark.parametrize("name", LONG_K_CASES)
+def test_gemm_long_k_fixtures_every_schedule(gk, golden_gemm, gemm_cases, name):
+    # the long-K shapes of the reference's simulator test (tests/fp8_hybrid_tpcsim_test.cpp:388-392): 56, 28 and 172
+    # K blocks per output, where a barrier-phase or scale-prefetch slip of a persistent kernel would show; run
+    # through the large-tile, the small-M and the CTA-pair schedules against fixtures the reference produced
+    c = gemm_cases[name]
+    x, w, s, b = _case_tensors(c)
+    for half in (False, True):
+        want = torch.from_numpy(golden_gemm[f"{name}.y_bits.half{int(half)}"]).view(torch.bfloat16)
+        y64, ybf = block_fp8_ref.reference_rows(x, w, s, native_half=half, bias=b)
+        assert torch.equal(ybf, want)
+        rms = float(y64.pow(2).mean().sqrt())
+        a_codes, a_scales = gk.quantize_act_1x128(x.cuda(), native_half=half)
+        wc, ws = gk.prepare_weight(w, s, native_half=half)
+        outs = {}
+        for schedule, cap in ((1, 0), (1, 1), (2, 0), (2, 3), (3, 0)):
+            out = gk.gemm_block_fp8(a_codes, a_scales, wc, ws, out_dtype=torch.float32, schedule=schedule, max_ctas=cap)
+            err = float((out.double().cpu() - y64).abs().max())
+            assert err / rms <= TOL, (name, half, schedule, cap, err / rms)
+            out16 = gk.gemm_block_fp8(a_codes, a_scales, wc, ws, schedule=schedule, max_ctas=cap)
+            assert torch.equal(out16, out.to(torch.bfloat16))
+            assert_bf16_close(out16.cpu(), want, err, (name, half, schedule))
+            num = (out16.double().cpu() - want.double()).pow(2).sum(1).sqrt()
+            den = want.double().pow(2).sum(1).sqrt()
+            assert bool((num[den > 0] / den[den > 0] <= 0.01).all()) and bool((num[den == 0] == 0).all())
+            outs[(schedule, cap)] = out
+        assert torch.equal(outs[(1, 0)], outs[(1, 1)]) and torch.equal(outs[(1, 0)], outs[(3, 0)])
+
+
+def _row_sample_check(gk, x, a_codes, a_scales, wc, ws, w_ocp, s_ocp, g, rows=48, **kw):
+    """Full-size launch checked on a seeded sample of rows against the oracle; returns the fp32 output."""
+    m = x.shape[0]
+    out16 = gk.gemm_block_fp8(a_codes, a_scales, wc, ws, **kw)
+    out32 = gk.gemm_block_fp8(a_codes, a_scales, wc, ws, out_dtype=torch.float32, **kw)
+    assert torch.equal(out16, out32.to(torch.bfloat16))
+    pick = torch.randperm(m, generator=g)[:rows].sort().values
+    y64, ybf = block_fp8_ref.reference_rows(x[pick], w_ocp.cpu(), s_ocp.cpu(), native_half=True)
+    rms = float(y64.pow(2).mean().sqrt())
+    err = float((out32[pick.cuda()].double().cpu() - y64).abs().max())
+    assert err / rms <= TOL
+    assert_bf16_close(out16[pick.cuda()].cpu(), ybf, err)
+    num = (out16[pick.cuda()].double().cpu() - ybf.double()).pow(2).sum(1).sqrt()
+    assert bool((num / ybf.double().pow(2).sum(1).sqrt() <= 0.01).all())
+    return out32
+
+
+def test_gemm_prefill_down_shape_row_sample(gk):
+    # the other prefill shape, M=8192, K=14336, N=4096 (112 K blocks per output), at full size
+    m, k, n = 8192, 14336, 4096
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn((m, k), generator=g).to(torch.bfloat16)
+    wf = (torch.randn((n, k), generator=g) * 0.02).cuda()
+    w_ocp, s_ocp = gk.quantize_block128(wf)
+    del wf
+    wc, ws = gk.prepare_weight(w_ocp, s_ocp, native_half=True)
+    a_codes, a_scales = gk.quantize_act_1x128(x.cuda(), native_half=True)
+    out32 = _row_sample_check(gk, x, a_codes, a_scales, wc, ws, w_ocp, s_ocp, g)
+    out_2x = gk.gemm_block_fp8(a_codes, a_scales, wc, ws * 2, out_dtype=torch.float32)
+    assert torch.equal(out_2x, out32 * 2)
+
+
+def test_gemm_ffn70b_rank_slice_row_sample(gk):
+    # one rank's share of the 8-GPU column-sharded shape: M=16384, K=8192, rank 3's 3584 of N=28672 columns,
+    # cut from the full prepared weight by sharded.shard_weight (non-zero row offset into codes and scale grid)
+    from gaudi_kernels_b200 import sharded
+    m, k, n, world, rank = 16384, 8192, 28672, 8, 3
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn((m, k), generator=g).to(torch.bfloat16)
+    gw = torch.Generator(device="cuda").manual_seed(3)
+    w_ocp = torch.empty((n, k), dtype=torch.float8_e4m3fn, device="cuda")
+    s_ocp = torch.empty((n // 128, k // 128), dtype=torch.float32, device="cuda")
+    for r0 in range(0, n, 3584):                                             # quantized slice by slice to bound fp32 memory
+        wf = torch.randn((3584, k), generator=gw, device="cuda") * 0.02
+        c, s = gk.quantize_block128(wf)
+        w_ocp[r0:r0 + 3584] = c
+        s_ocp[r0 // 128:(r0 + 3584) // 128] = s
+        del wf
+    wc, ws = gk.prepare_weight(w_ocp, s_ocp, native_half=True)
+    wl, sl = sharded.shard_weight(wc, ws, world, rank)
+    lo, hi = sharded.shard_bounds(n, world, rank)
+    assert (lo, hi) == (3 * 3584, 4 * 3584) and wl.data_ptr() == wc.data_ptr() + lo * k
+    a_codes, a_scales = gk.quantize_act_1x128(x.cuda(), native_half=True)
+    _row_sample_check(gk, x, a_codes, a_scales, wl.contiguous(), sl.contiguous(), w_ocp[lo:hi], s_ocp[lo // 128:hi // 128], g)
+    # the views themselves (no copy): what sharded.gemm_sharded is given
+    out_view = sharded.gemm_sharded(a_codes, a_scales, wl, sl)
+    out_copy = gk.gemm_block_fp8(a_codes, a_scales, wl.contiguous(), sl.contiguous())
+    assert torch.equal(out_view, out_copy)
