@@ -63,8 +63,26 @@ def _group_major(a_scales, m, g):
     return t, m
 
 
+def wait_timed_out(status):
+    """True if a kernel given `status` (a tensor from new_status()) reported an expired bounded wait.
+
+    Reads the word back (one synchronisation with the launching stream).  After a time-out the small-M schedule's
+    arrival counters may be non-zero, so the cached workspaces are dropped; the outputs of the calls that shared
+    the status word are invalid.
+    """
+    timed_out = bool(_read_status(status)[1] & _lib.STATUS_WAIT_TIMEOUT)
+    if timed_out:
+        _workspaces.clear()
+    return timed_out
+
+
+def new_status(device):
+    """A zeroed device status buffer for gemm_block_fp8(..., check=False, status=...); poll it with wait_timed_out."""
+    return _status_buffer(device)
+
+
 def gemm_block_fp8(a_codes, a_scales, w_codes, w_scales, bias=None, out=None, out_dtype=torch.bfloat16,
-                   check=True, schedule=0, max_ctas=0, wait_limit_cycles=0):
+                   check=True, schedule=0, max_ctas=0, wait_limit_cycles=0, status=None):
     """out[i, j] = sum_g a_scales[i, g] * w_scales[j // 128, g] * <a_codes[i, g-block], w_codes[j, g-block]> (+ bias[j]).
 
     a_codes  E4M3 [M, K] (float8_e4m3fn or uint8), contiguous, on a CUDA device
@@ -72,7 +90,10 @@ def gemm_block_fp8(a_codes, a_scales, w_codes, w_scales, bias=None, out=None, ou
     w_codes  E4M3 [N, K], contiguous;  w_scales fp32 [ceil(N/128), G] contiguous
     bias     fp32 [N] or None;  out_dtype torch.bfloat16 (default) or torch.float32
     check    read the device status word after the launch (one synchronisation) and raise if a
-             bounded wait expired; pass False on a latency-critical path and poll the status yourself
+             bounded wait expired; pass False on a latency-critical path together with `status`
+    status   a buffer from new_status() that receives the kernel's status bits; several calls may share one.
+             With check=False the caller reads it later through wait_timed_out(status).  Without a status
+             buffer an unchecked call cannot report an expired wait.
     """
     for name, t in (("a_codes", a_codes), ("w_codes", w_codes)):
         if (not isinstance(t, torch.Tensor) or t.dtype not in (torch.float8_e4m3fn, torch.uint8) or t.ndim != 2
@@ -114,7 +135,7 @@ def gemm_block_fp8(a_codes, a_scales, w_codes, w_scales, bias=None, out=None, ou
             ldo = out.stride(0)
         ws_bytes = lib.bfp8_gemm_block128_workspace_bytes(m, n, k)
         ws = _workspace(dev, ws_bytes) if ws_bytes else None
-        st = _status_buffer(dev)
+        st = status if status is not None else _status_buffer(dev)
         rc = lib.bfp8_gemm_block128_ex(
             a_codes.data_ptr(), lda, sa.data_ptr(), ldsa, w_codes.data_ptr(), ldw, w_scales.data_ptr(),
             bias.data_ptr() if bias is not None else None, out.data_ptr(),
@@ -318,10 +339,12 @@ def reference(x, weight, scales, *, native_half=False, bias=None, out_dtype=torc
             rc = lib.bfp8_reencode_half(wd.data_ptr(), enc.data_ptr(), wd.numel(), sd.data_ptr(), sw.data_ptr(),
                                         sd.numel(), st.data_ptr(), st.data_ptr() + 8, _stream_ptr())
             _lib.check(rc, "bfp8_reencode_half")
-            finite = None
         else:
+            # block_fp8_oracle.py:22-24: the same rejections, without changing the codes
             enc, sw = wd, sd
-            finite = ((wd.view(torch.uint8) & 0x7F) != 0x7F).all() & torch.isfinite(sd).all() & (sd >= 0).all()
+            rc = lib.bfp8_validate_e4m3(wd.data_ptr(), wd.numel(), sd.data_ptr(), sd.numel(), st.data_ptr() + 8,
+                                        _stream_ptr())
+            _lib.check(rc, "bfp8_validate_e4m3")
         m = x.shape[0]
 
         def run_rows(x_rows, dev_out):
@@ -334,7 +357,7 @@ def reference(x, weight, scales, *, native_half=False, bias=None, out_dtype=torc
                                                st.data_ptr() + 8, _stream_ptr())
             _lib.check(rc, "bfp8_quant_act_1x128_bf16")
             return gemm_block_fp8(a_codes, a_scales.t(), enc, sw, bias=bias, out=dev_out, out_dtype=out_dtype,
-                                  check=False)
+                                  check=False, status=st)
 
         if not on_host:
             dev_out = out if (out is not None and out.device.type == "cuda") else None
@@ -365,8 +388,9 @@ def reference(x, weight, scales, *, native_half=False, bias=None, out_dtype=torc
             main.wait_stream(side)
             y = out
         status = _read_status(st)[1]               # synchronises: also completes the copy above
-        if finite is not None and not bool(finite):
-            status |= _lib.STATUS_NONFINITE_CODE
         if status & (_lib.STATUS_NONFINITE_CODE | _lib.STATUS_BAD_SCALE | _lib.STATUS_NONFINITE_INPUT):
             raise ValueError("finite original inputs required")
+        if status & _lib.STATUS_WAIT_TIMEOUT:
+            _workspaces.clear()            # arrival counters may have been left non-zero
+            raise _lib.Bfp8Error(_WAIT_TIMEOUT_MSG)
     return y

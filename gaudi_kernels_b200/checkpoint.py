@@ -9,8 +9,10 @@ for a fused gate/up weight, the 64-row interleave of the SwiGLU kernel).  What i
 host-to-device copy: `stream_checkpoint` stages tensor t + 1 into pinned memory and copies it over PCIe on
 a side stream while tensor t is re-encoded, and reads all status words once at the end.
 
-Every check of `reencode_e4m3fn_half` still applies (0x7f / 0xff codes, scales that are negative,
-non-finite or overflow when doubled); a violation raises ValueError naming the tensor.
+Every check of `reencode_e4m3fn_half` still applies (0x7f / 0xff codes, scales that are negative or
+non-finite, and - where the scales are doubled, native_half=True - scales that overflow when doubled);
+a violation raises ValueError naming the tensor.  With native_half=False the codes are kept as they are and
+a read-only kernel (bfp8_validate_e4m3) makes the checks.
 """
 
 import torch
@@ -145,6 +147,10 @@ def stream_checkpoint(entries, device=None, native_half=True, swiglu=(), staging
                 main.wait_event(landed)
                 dev_w.record_stream(copy)
                 dev_s.record_stream(copy)
+                # the codes stay as they are, the checks of fp8_codec.py:25-29,48-49 still apply
+                rc = lib.bfp8_validate_e4m3(dev_w.data_ptr(), w_bytes, dev_s.data_ptr(), scales.numel(),
+                                            st.data_ptr() + 8, _stream_ptr())
+                _lib.check(rc, "bfp8_validate_e4m3")
             if name in swiglu:
                 if n % (2 * BLOCK) != 0:
                     raise ValueError("%s: fused gate/up weight must be [2 * I, K] with I a multiple of 128" % name)

@@ -114,6 +114,38 @@ reencode_half_kernel(const uint8_t* in, uint8_t* out, int64_t n, int vec_ok,    
   }
 }
 
+// Read-only form of the checks above for checkpoints that are used as they are (OCP codes, no half-range
+// step): any 0x7f / 0xff code, any negative or non-finite scale.  Grid-stride, 16 bytes per thread and step.
+__global__ void __launch_bounds__(256)
+validate_e4m3_kernel(const uint8_t* __restrict__ codes, int64_t n, int vec_ok, const float* __restrict__ scales,
+                     int64_t n_scales, uint32_t* __restrict__ status) {
+  const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t nthreads = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  uint32_t bad = 0;
+  if (vec_ok) {
+    const int64_t nvec = n >> 4;
+    const uint4* v = reinterpret_cast<const uint4*>(codes);
+    for (int64_t i = tid; i < nvec; i += nthreads) {
+      const uint4 x = __ldcs(v + i);
+      bad |= nonfinite_x4(x.x) | nonfinite_x4(x.y) | nonfinite_x4(x.z) | nonfinite_x4(x.w);
+    }
+    for (int64_t i = (nvec << 4) + tid; i < n; i += nthreads) bad |= nonfinite_x4(codes[i]) & 0xffu;
+  } else {
+    for (int64_t i = tid; i < n; i += nthreads) bad |= nonfinite_x4(codes[i]) & 0xffu;
+  }
+  bool bad_scale = false;
+  for (int64_t i = tid; i < n_scales; i += nthreads) {
+    const float sc = scales[i];
+    bad_scale |= !(sc >= 0.0f) || isinf(sc);
+  }
+  bad = __reduce_or_sync(0xffffffffu, bad);
+  const uint32_t bs = __reduce_or_sync(0xffffffffu, bad_scale ? 1u : 0u);
+  if ((threadIdx.x & 31) == 0) {
+    if (bad) atomicOr(status, BFP8_STATUS_NONFINITE_CODE);
+    if (bs) atomicOr(status, BFP8_STATUS_BAD_SCALE);
+  }
+}
+
 // ---------------------------------------------------------------------------------------------
 // K2  128x128 block-amax quantizer: one CTA per tile, the 64 KB tile lives in registers
 //     (256 threads x 16 float4), so HBM sees exactly one read and one write per element.
@@ -191,8 +223,7 @@ constexpr int kActSlots = kActThreads / kActLanes * kActPer;   // group slots pe
 // silu(g) * u of csrc/tpc/generic_dense/silu_and_mul_bf16.c:4-13, rounded to bf16 as that kernel stores it; the
 // same expression as the GEMM's fused epilogue and the stand-alone kernel, so all three agree bit for bit.
 __device__ __forceinline__ float silu_mul_bf16_rounded(float g, float u) {
-  const float q = __fdividef(g, 1.0f + __expf(-g));
-  return bf16_bits_to_float(float_to_bf16_bits((g <= -88.0f ? 0.0f : q) * u));
+  return bf16_bits_to_float(float_to_bf16_bits(silu_mul(g, u)));
 }
 
 // kSilu: x is a gate/up pair [m, 2 k] (gate columns, then up columns, row pitch ldx) and the values quantized are
@@ -598,7 +629,7 @@ extern "C" const char* bfp8_error_string(int code) {
     case BFP8_ERR_SHAPE: return "size out of range";
     case BFP8_ERR_WORKSPACE: return "workspace too small";
     case BFP8_ERR_CUDA: return "CUDA call failed";
-    case BFP8_ERR_UNSUPPORTED: return "device is not sm_100";
+    case BFP8_ERR_UNSUPPORTED: return "not an sm_100 device, or a shape / configuration this entry point does not take";
     case BFP8_ERR_TOO_LARGE: return "problem exceeds the fixed scratch of the no-allocation entry point";
     default: return "unknown error";
   }
@@ -619,6 +650,19 @@ extern "C" int bfp8_reencode_half(const uint8_t* codes_in, uint8_t* codes_out, i
   const int grid = static_cast<int>(ctas);
   reencode_half_kernel<<<grid, kReencodeThreads, 0, st>>>(codes_in, codes_out, n, vec_ok, scales_in, scales_out, n_scales,
                                                           rounded_dev, status_dev);
+  BFP8_CUDA_TRY(cudaGetLastError());
+  return BFP8_OK;
+}
+
+extern "C" int bfp8_validate_e4m3(const uint8_t* codes, int64_t n, const float* scales, int64_t n_scales,
+                                  uint32_t* status_dev, void* stream) {
+  if (!codes || !status_dev) return BFP8_ERR_NULL;
+  if (n <= 0 || n_scales < 0) return BFP8_ERR_SHAPE;
+  if (n_scales > 0 && !scales) return BFP8_ERR_NULL;
+  if (!aligned(status_dev, 4) || (scales && !aligned(scales, 4))) return BFP8_ERR_ALIGN;
+  const int64_t want = ((n >> 4) + 255) / 256 + 1, cap = static_cast<int64_t>(sm_count()) * 8;
+  validate_e4m3_kernel<<<static_cast<unsigned>(want < cap ? want : cap), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      codes, n, aligned(codes, 16) ? 1 : 0, scales, n_scales, status_dev);
   BFP8_CUDA_TRY(cudaGetLastError());
   return BFP8_OK;
 }

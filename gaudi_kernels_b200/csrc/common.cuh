@@ -195,6 +195,22 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   return r;
 }
 
+// silu(g) * u as csrc/tpc/generic_dense/silu_and_mul_bf16.c:4-13 defines it: denom = 1 + exp(-g); the quotient
+// g / denom is an approximate reciprocal refined by one residual step (q = g * inv; q += fma(-q, denom, g) * inv,
+// :6-9), exactly 0 for g <= -88 (:10), and a NaN gate is passed through by bit pattern (:11-12).  The refined
+// quotient is the correctly rounded one except in rare last-bit cases; what is left against an exact evaluation
+// is the error of ex2.approx in exp(-g).
+__device__ __forceinline__ float silu_mul(float g, float u) {
+  const float denom = 1.0f + __expf(-g);
+  float inv;
+  asm("rcp.approx.f32 %0, %1;" : "=f"(inv) : "f"(denom));
+  const float q = g * inv;
+  const float refined = __fmaf_rn(__fmaf_rn(-q, denom, g), inv, q);
+  float val = g <= -88.0f ? 0.0f : refined;
+  if ((__float_as_uint(g) & 0x7fffffffu) > 0x7f800000u) val = g;
+  return val * u;
+}
+
 // 64 output columns of one row as bf16 with plain stores, only the first `valid` of them.  Used for the
 // last box of a row when N is not a multiple of 8: a bulk tensor store writes whole 16-byte chunks.
 __device__ __forceinline__ void store_row_bf16_guarded(uint16_t* o, const float2* a, int valid) {

@@ -163,12 +163,6 @@ extern "C" int bfp8_gemm_block128_swiglu(const uint8_t* a_codes, int64_t lda, co
 // ---- the SwiGLU step on its own, for results of the schedules that have no fused form (decode bucket) -------
 
 namespace {
-// Same arithmetic as the fused epilogue of gemm_tcgen05.cu (silu_and_mul_bf16.c:4-13).
-__device__ __forceinline__ float silu_mul_f32(float g, float u) {
-  const float q = __fdividef(g, 1.0f + __expf(-g));
-  return (g <= -88.0f ? 0.0f : q) * u;
-}
-
 // One 16-byte vector (8 outputs) per thread and iteration; gate at column c, up at column c + inter of a row.
 __global__ void __launch_bounds__(256)
 silu_and_mul_kernel(const uint16_t* __restrict__ gate_up, int64_t ld_in, uint16_t* __restrict__ out, int64_t ld_out,
@@ -188,8 +182,8 @@ silu_and_mul_kernel(const uint16_t* __restrict__ gate_up, int64_t ld_in, uint16_
       uint32_t o[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j)
-        o[j] = pack_bf16x2(silu_mul_f32(bf16_lo_to_float(gw[j]), bf16_lo_to_float(uw[j])),
-                           silu_mul_f32(bf16_hi_to_float(gw[j]), bf16_hi_to_float(uw[j])));
+        o[j] = pack_bf16x2(silu_mul(bf16_lo_to_float(gw[j]), bf16_lo_to_float(uw[j])),
+                           silu_mul(bf16_hi_to_float(gw[j]), bf16_hi_to_float(uw[j])));
       __stcs(reinterpret_cast<uint4*>(out + r * ld_out) + v, make_uint4(o[0], o[1], o[2], o[3]));
     }
   } else {
@@ -198,7 +192,7 @@ silu_and_mul_kernel(const uint16_t* __restrict__ gate_up, int64_t ld_in, uint16_
          i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
       const int64_t r = i / inter, c = i - r * inter;
       const float g = bf16_bits_to_float(gate_up[r * ld_in + c]), u = bf16_bits_to_float(gate_up[r * ld_in + inter + c]);
-      out[r * ld_out + c] = static_cast<uint16_t>(float_to_bf16_bits(silu_mul_f32(g, u)));
+      out[r * ld_out + c] = static_cast<uint16_t>(float_to_bf16_bits(silu_mul(g, u)));
     }
   }
 }

@@ -184,7 +184,8 @@ gemm_channel_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       const bool row_ok = row < p.m;
       const float act = row_ok ? __ldg(p.a_scales + row) : 0.0f;
       const uint32_t buf = it & 1u, acc_phase = (it >> 1) & 1u;
-      ok = ptx::mbar_wait(ptx::smem_u32(&tail->tmem_full[buf]), acc_phase, abort_flag, p.wait_limit);
+      // uniform across the warp: warp-collective TMEM loads follow
+      ok = __all_sync(0xffffffffu, ptx::mbar_wait(ptx::smem_u32(&tail->tmem_full[buf]), acc_phase, abort_flag, p.wait_limit));
       if (!ok) break;
       ptx::tc_fence_after_sync();
       const uint32_t taddr = tmem_base + lane_addr + buf * BN + wg * 128;

@@ -215,7 +215,9 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         const long long u = base + i;
         if (u < u1 && ok) {
           const uint32_t buf = kb % kAccBufs, acc_phase = (kb / kAccBufs) & 1u;
-          ok = ptx::mbar_wait(ptx::smem_u32(&tail->tmem_empty[buf]), acc_phase ^ 1u, abort_flag, p.wait_limit);
+          // the outcome is made uniform across the warp before the warp-wide barrier below
+          ok = __all_sync(0xffffffffu, ptx::mbar_wait(ptx::smem_u32(&tail->tmem_empty[buf]), acc_phase ^ 1u, abort_flag,
+                                                      p.wait_limit));
           if (ok) {
 #pragma unroll
             for (int q = 0; q < kPer; ++q)
@@ -240,12 +242,19 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     long long seg_start = u0;
     bool ok = true;
     int tile = static_cast<int>(u0 / G), g = static_cast<int>(u0 % G) - 1;
-    for (long long u = u0; u < u1 && ok; ++u, ++kb) {
+    // A thread whose bounded wait expired does not leave the loop in the plain form: the four epilogue warps meet
+    // at named barriers at every segment end, so it keeps walking the units (without waiting or touching TMEM)
+    // and takes part in those barriers; its siblings see the abort flag at their next wait and do the same.
+    for (long long u = u0; u < u1 && (ok || !kCluster); ++u, ++kb) {
       if (++g == G) { g = 0; ++tile; }
       const uint32_t buf = kb % kAccBufs, acc_phase = (kb / kAccBufs) & 1u;
-      ok = ptx::mbar_wait(ptx::smem_u32(&tail->tmem_full[buf]), acc_phase, abort_flag, p.wait_limit) &&
-           ptx::mbar_wait(ptx::smem_u32(&tail->scale_full[buf]), acc_phase, abort_flag, p.wait_limit);
-      if (!ok) break;
+      if (ok) {
+        // uniform across the warp before the warp-collective TMEM loads
+        ok = __all_sync(0xffffffffu,
+                        ptx::mbar_wait(ptx::smem_u32(&tail->tmem_full[buf]), acc_phase, abort_flag, p.wait_limit) &&
+                        ptx::mbar_wait(ptx::smem_u32(&tail->scale_full[buf]), acc_phase, abort_flag, p.wait_limit));
+      }
+      if (ok) {
       ptx::tc_fence_after_sync();
       const uint32_t taddr = tmem_base + lane_addr + buf * MP;
       constexpr int kChunk = MP < 64 ? MP : 64;                  // columns fetched per TMEM round trip
@@ -272,6 +281,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
       ptx::tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&tail->tmem_empty[buf]));
+      }
 
       if (!kCluster && (g == G - 1 || u == u1 - 1)) {
         // ---- end of this CTA's segment of the tile
@@ -311,7 +321,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
           }
           asm volatile("bar.sync 1, 128;" ::: "memory");          // last_flag may be rewritten next segment
         }
-        if (do_store && col < p.n) {
+        if (do_store && ok && col < p.n) {
           const float b = p.bias != nullptr ? __ldg(p.bias + col) : 0.0f;
           if (p.out_bf16) {
             uint16_t* o = reinterpret_cast<uint16_t*>(p.out) + col;
@@ -554,20 +564,15 @@ constexpr size_t kNoAllocScratchBytes =
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
 
 // Device address of the scratch array on the current device.  In host code the array's name is only a
-// handle for the runtime, never a pointer a kernel may use, so the address is asked for once per device
-// (with that device current) and remembered.
+// handle for the runtime, never a pointer a kernel may use, so the address is asked for with that device
+// current.  The lookup is a host-side table query and is repeated on every call rather than cached: a cached
+// address would be wrong after the device's context has been destroyed and re-created (cudaDeviceReset), and a
+// shared cache would need synchronisation between host threads.
 int noalloc_scratch_address(void** out) {
-  static void* address[64] = {};
-  int dev = 0;
-  BFP8_CUDA_TRY(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64) return BFP8_ERR_UNSUPPORTED;
-  if (address[dev] == nullptr) {
-    void* p = nullptr;
-    BFP8_CUDA_TRY(cudaGetSymbolAddress(&p, g_noalloc_scratch));
-    if (p == nullptr) return BFP8_ERR_CUDA;
-    address[dev] = p;
-  }
-  *out = address[dev];
+  void* p = nullptr;
+  BFP8_CUDA_TRY(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+  if (p == nullptr) return BFP8_ERR_CUDA;
+  *out = p;
   return BFP8_OK;
 }
 
@@ -582,8 +587,8 @@ int noalloc_scratch_address(void** out) {
 //
 // Same arguments and results as bfp8_gemm_block128 (minus the workspace), for m <= 32 and
 // n <= 2,097,152.  Larger problems return BFP8_ERR_TOO_LARGE and launch nothing.  The call performs no
-// cudaMalloc / cudaFree and uses no allocating library routine.  The first call on each device looks up
-// the scratch array's device address and raises the kernel's shared-memory limit; make that first call
+// cudaMalloc / cudaFree and uses no allocating library routine.  Every call asks the runtime for the scratch
+// array's device address; the first call on each device also raises the kernel's shared-memory limit; make it
 // before any stream capture.  All calls on a device share the one array: the counters are cleared on the
 // stream at the start of every call (the partial sums need no clearing, they are written before they are
 // read), and two calls that may overlap on the GPU - different streams, or different host threads - race

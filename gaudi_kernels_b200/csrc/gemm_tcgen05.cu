@@ -98,13 +98,6 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
   tn = r / rows;
 }
 
-// silu(g) * u as csrc/tpc/generic_dense/silu_and_mul_bf16.c:4-13 defines it: g / (1 + exp(-g)), exactly 0 for
-// g <= -88, NaN passed through.  The fast division flushes quotients below 2^-126 (g in (-88, -87.3)) to zero.
-__device__ __forceinline__ float silu_mul(float g, float u) {
-  const float q = __fdividef(g, 1.0f + __expf(-g));
-  return (g <= -88.0f ? 0.0f : q) * u;
-}
-
 // kSwiGLU: W holds gate and up rows interleaved in chunks of 64 (bfp8_swiglu_interleave_weight), so the 128
 // tile columns of a warpgroup are 64 gate columns followed by the 64 up columns of the same outputs, and a
 // thread ends a tile holding both factors of its 64 outputs.  The tile's 256 weight rows are outputs
@@ -237,7 +230,9 @@ gemm_block128_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       uint32_t ra[32], rb[32];
       {
         const uint32_t buf = kb & 1u;
-        ok = ptx::mbar_wait(ptx::smem_u32(&tail->done[kb & (kStages - 1)]), (kb >> 2) & 1u, abort_flag, p.wait_limit);
+        // wait outcomes are made uniform across the warp: warp-collective TMEM loads and __syncwarp follow them
+        ok = __all_sync(0xffffffffu, ptx::mbar_wait(ptx::smem_u32(&tail->done[kb & (kStages - 1)]), (kb >> 2) & 1u,
+                                                    abort_flag, p.wait_limit));
         if (!ok) break;
         ptx::tc_fence_after_sync();
         const uint32_t taddr = tmem_base + lane_addr + buf * BN + wg * 128;
@@ -288,7 +283,8 @@ gemm_block128_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         if (g + 1 < G) {
           // first half of the next K block's buffer
           const uint32_t nkb = kb + 1, nbuf = nkb & 1u;
-          ok = ptx::mbar_wait(ptx::smem_u32(&tail->done[nkb & (kStages - 1)]), (nkb >> 2) & 1u, abort_flag, p.wait_limit);
+          ok = __all_sync(0xffffffffu, ptx::mbar_wait(ptx::smem_u32(&tail->done[nkb & (kStages - 1)]), (nkb >> 2) & 1u,
+                                                      abort_flag, p.wait_limit));
           if (!ok) break;
           ptx::tc_fence_after_sync();
             const uint32_t naddr = tmem_base + lane_addr + nbuf * BN + wg * 128;

@@ -118,8 +118,11 @@ class PeerExchange:
         _lib.check(rc, "bfp8_peer_barrier")
 
     def timed_out(self):
-        """True if a barrier wait expired (reads the status word: one synchronisation)."""
-        return bool(int(self.status.cpu()[2]) & _lib.STATUS_WAIT_TIMEOUT)
+        """True if a bounded wait expired in a barrier or in a GEMM launched by gemm_k_sharded (reads the status
+        word: one synchronisation).  The cached small-M workspaces are dropped then: their arrival counters may
+        have been left non-zero."""
+        from .block_fp8_gemm import wait_timed_out
+        return wait_timed_out(self.status)
 
     def close(self):
         if self._own is None:
@@ -191,7 +194,9 @@ def gemm_k_sharded(a_codes_local, a_scales_local, w_codes_local, w_scales_local,
              (bfp8_gemm_block128_push), so the exchange overlaps the math; after the barrier each rank holds the
              `gathered` layout of rank_sum.c and sums it locally.  Needs M % (128 * world) == 0, N % 64 == 0.
     unfused  the partial is written locally in `partial_dtype` (bf16 or fp32) and reduce_scatter_rows reads the
-             peers' rows over NVLink.  Any shape.
+             peers' rows over NVLink.  fp32 partials take any shape; bf16 partials need N % 8 == 0 (their rows are
+             stored in 16-byte units, BFP8_ERR_ALIGN otherwise).
+    Either form reports an expired bounded wait (GEMM or barrier) through exchange.timed_out().
     fused=None picks the fused form where it applies.
     """
     from .block_fp8_gemm import _group_major, gemm_block_fp8
@@ -206,7 +211,7 @@ def gemm_k_sharded(a_codes_local, a_scales_local, w_codes_local, w_scales_local,
     if not fused:
         partial = exchange.partial(m, n, partial_dtype)
         gemm_block_fp8(a_codes_local, a_scales_local, w_codes_local, w_scales_local, out=partial,
-                       out_dtype=partial_dtype, check=False)
+                       out_dtype=partial_dtype, check=False, status=exchange.status)
         return reduce_scatter_rows(exchange, partial, bias=bias, out=out)
 
     rows = m // world

@@ -36,10 +36,16 @@ def shard_weight(w_codes, w_scales, world, rank):
     return w_codes[start:stop], w_scales[start // BLOCK:(stop + BLOCK - 1) // BLOCK]
 
 
-def gemm_sharded(a_codes, a_scales, w_codes_local, w_scales_local, bias_local=None, out=None):
-    """This rank's [M, N_local] slice of the product (no communication)."""
+def gemm_sharded(a_codes, a_scales, w_codes_local, w_scales_local, bias_local=None, out=None, status=None):
+    """This rank's [M, N_local] slice of the product (no communication).
+
+    The launch is not followed by a synchronisation.  Pass `status` (block_fp8_gemm.new_status(device), shared by
+    as many calls as you like) and test it with block_fp8_gemm.wait_timed_out(status) once the step is complete:
+    a kernel whose bounded wait expired reports it there and its output is invalid.
+    """
     from .block_fp8_gemm import gemm_block_fp8
-    return gemm_block_fp8(a_codes, a_scales, w_codes_local, w_scales_local, bias=bias_local, out=out, check=False)
+    return gemm_block_fp8(a_codes, a_scales, w_codes_local, w_scales_local, bias=bias_local, out=out, check=False,
+                          status=status)
 
 
 def gather_columns(local_out, group=None):

@@ -62,6 +62,13 @@ int bfp8_reencode_half(const uint8_t* codes_in, uint8_t* codes_out, int64_t n,
                        const float* scales_in, float* scales_out, int64_t n_scales,
                        unsigned long long* rounded_dev, uint32_t* status_dev, void* stream);
 
+/* The input checks of bfp8_reencode_half without the re-encoding, for checkpoints whose OCP codes are used
+ * unchanged: status |= NONFINITE_CODE for any 0x7f / 0xff code (python/gaudi_kernels/fp8_codec.py:48-49;
+ * python/gaudi_kernels/block_fp8_oracle.py:22-24 rejects the same inputs), BAD_SCALE for a negative or
+ * non-finite scale (fp8_codec.py:25-29).  Nothing is written but the status word.  n > 0; n_scales may be 0. */
+int bfp8_validate_e4m3(const uint8_t* codes, int64_t n, const float* scales, int64_t n_scales,
+                       uint32_t* status_dev, void* stream);
+
 /* 128x128 block-amax quantizer, fp32 [rows, cols] (row stride ld, elements) -> E4M3 codes
  * [rows, cols] (row stride ld_codes) + fp32 scales [ceil(rows/128), ceil(cols/128)] (dense).
  * Per tile: scale = max(amax, 1e-10) * fp32(1/448); code = RNE_e4m3(clamp(x / scale, +-448)) -
@@ -108,10 +115,11 @@ int bfp8_decode_block128(const uint8_t* codes, int64_t rows, int64_t cols, int64
  * mean the same values under that format.  Each 128-wide block dot product is accumulated by the
  * tensor core in fp32 (TMEM); the promotion across K blocks is an fp32 FMA chain in g order.
  * workspace: bfp8_gemm_block128_workspace_bytes(m, n, k) bytes, 256-byte aligned (may be NULL if 0).
- *   Its first 64 KB hold arrival counters: they must be zero before the first call and every call
- *   leaves them zero, so one zero-initialised buffer serves any sequence of calls on one stream.
- *   Calls that may overlap on the device need separate workspaces.
- * status |= WAIT_TIMEOUT if an internal barrier wait gave up (output is then undefined). */
+ *   Its first 64 KB hold arrival counters: they must be zero before the first call and every call that
+ *   completes normally leaves them zero, so one zero-initialised buffer serves any sequence of calls on
+ *   one stream.  Calls that may overlap on the device need separate workspaces.
+ * status |= WAIT_TIMEOUT if an internal barrier wait gave up; the output is then undefined and counters may
+ *   have been left non-zero: zero the first 64 KB of the workspace again before it is reused. */
 size_t bfp8_gemm_block128_workspace_bytes(int64_t m, int64_t n, int64_t k);
 int bfp8_gemm_block128(const uint8_t* a_codes, int64_t lda, const float* a_scales, int64_t ldsa,
                        const uint8_t* w_codes, int64_t ldw, const float* w_scales,
@@ -165,8 +173,9 @@ int bfp8_gemm_token_channel(const uint8_t* a_codes, int64_t lda, const float* a_
  * every GPU that loads it), so the size is limited: m <= 32 and n <= 2,097,152, otherwise
  * BFP8_ERR_TOO_LARGE is returned and nothing is launched.  Arguments and results are those of
  * bfp8_gemm_block128 without the workspace.  No cudaMalloc / cudaFree or allocating library routine
- * is called.  The first call on a device performs one-time set-up (it looks up the array's device
- * address and raises the kernel's shared-memory limit) and should be made before any stream capture.
+ * is called.  Every call asks the runtime for the array's device address (a host-side query, made with the
+ * call's device current); the first call on a device also loads the library's device code and raises the
+ * kernel's shared-memory limit, so make that first call before any stream capture.
  * All calls on a device share the array: calls that may overlap on the GPU race on it. */
 int bfp8_gemm_block128_noalloc(const uint8_t* a_codes, int64_t lda, const float* a_scales, int64_t ldsa,
                                const uint8_t* w_codes, int64_t ldw, const float* w_scales,

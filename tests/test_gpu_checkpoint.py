@@ -53,6 +53,17 @@ def test_streamed_checkpoint_equals_per_tensor_codec(gk):
     for name, (w, s) in tensors.items():
         assert torch.equal(plain[name][0].view(torch.uint8).cpu(), w.view(torch.uint8))
         assert torch.equal(plain[name][1].cpu(), s) and plain[name][2] == 0
+    # ... and still checked: a NaN code or a negative / non-finite scale is rejected, naming the tensor
+    name, (w, s) = next(iter(tensors.items()))
+    bad_w = w.view(torch.uint8).clone()
+    bad_w[-1, -1] = 0xFF
+    with pytest.raises(ValueError, match="nonfinite"):
+        stream_checkpoint([(name, bad_w.view(torch.float8_e4m3fn), s)], native_half=False)
+    for bad in (-1.0, float("inf"), float("nan")):
+        bad_s = s.clone()
+        bad_s.view(-1)[0] = bad
+        with pytest.raises(ValueError, match=name):
+            stream_checkpoint([(name, w, bad_s)], native_half=False)
 
 
 def test_streamed_checkpoint_swiglu_entry_and_errors(gk):

@@ -58,12 +58,20 @@ def test_noalloc_entry_point_matches_workspace_entry_point(m, k, n, out_dtype):
                                             w_scales.data_ptr(), bias.data_ptr(), out.data_ptr(), code, n, m, n, k,
                                             status.data_ptr(), stream)
         assert rc == 0
+    # the same schedule through the ordinary interface (weight-streaming form, at most 160 CTAs - the split the
+    # built-in scratch is sized for): the no-allocation call must reproduce it bit for bit
+    same = torch.empty((m, n), dtype=out_dtype, device="cuda")
+    rc = lib.bfp8_gemm_block128_ex(a_codes.data_ptr(), k, sa.data_ptr(), ldsa, w_codes.data_ptr(), k, w_scales.data_ptr(),
+                                   bias.data_ptr(), same.data_ptr(), code, n, m, n, k, ws.data_ptr(), ws_bytes,
+                                   status.data_ptr(), stream, 2, 160, 0)
+    assert rc == 0
     torch.cuda.synchronize()
     assert int(status.item()) == 0
     for out in outs:
         assert bool(torch.isfinite(out.float()).all())
         err = float((out.double() - want.double()).abs().max())
         assert err / rms <= TOL, err / rms
+        assert torch.equal(out, same)
 
 
 def test_noalloc_entry_point_rejects_sizes_beyond_its_scratch():
