@@ -71,6 +71,14 @@ def parse_args():
     return ap.parse_args()
 
 
+def make_config(workload, m, k, n, world):
+    """The `config` object of the JSON line; both arms (ours and --impl reference) print the same one."""
+    return {"workload": "%s M=%d K=%d N=%d" % (workload, m, k, n),
+            "sharding": "W rows (N) split over %d ranks, A replicated, output left sharded" % world if world > 1 else "single GPU",
+            "l2": "256 MiB buffer rewritten between timed steps (L2 is 126 MB); each step timed with its own CUDA events",
+            "timed": "GEMM on pre-quantized operands resident in HBM"}
+
+
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -225,6 +233,12 @@ def bench_codec(torch, lib, device, steps, warmup):
                                                            None, stream)) for i in range(len(xs))])
     nbytes = m * k * 3 + (k // 128) * m * 4
     out["quantize_act_1x128"] = {"ms": ms, "bytes": nbytes, "gbs": nbytes / ms / 1e6, "shape": "bf16 [8192, 4096]"}
+    # per-token quantizer (one scale per row): 2 B in + 1 B out per element + 4 B per row
+    tsc = torch.empty(m, dtype=torch.float32, device=device)
+    ms = timed([(lambda i=i: lib.bfp8_quant_act_token_bf16(xs[i].data_ptr(), m, k, k, xc[i].data_ptr(), k, tsc.data_ptr(), 1,
+                                                           None, stream)) for i in range(len(xs))])
+    nbytes = m * k * 3 + m * 4
+    out["quantize_act_token"] = {"ms": ms, "bytes": nbytes, "gbs": nbytes / ms / 1e6, "shape": "bf16 [8192, 4096]"}
     return out
 
 
@@ -363,16 +377,15 @@ def bench_checkpoint_stream(torch, device, tensors=12, n=8192, k=8192):
             "source": "pinned host memory"}
 
 
-def run_row_parallel(args, torch, dist, gk, device, workload, m, k, n, world, rank):
+def measure_row_parallel(torch, dist, gk, device, m, k, n, world, rank, steps, warmup, sample_clocks=True):
     """K-sharded down projection: every rank multiplies its K slice and the partials are added in rank order.
 
     Operands are drawn directly as codes (the quantizers are timed elsewhere).  A step is the fused form:
     GEMM whose epilogue stores its bf16 tiles into the owning GPU's memory, barrier, local rank-order sum, barrier.
-    The unfused form (local partial, then a sum kernel that reads the peers' rows) is timed beside it.
+    The unfused form (local partial, then a sum kernel that reads the peers' rows) and the GEMM alone are timed
+    beside it.  Returns a dict; every rank must call it.
     """
     from gaudi_kernels_b200 import row_parallel as rp
-    if world < 2:
-        raise SystemExit("ffn70b_down is a multi-GPU workload: start it with torch.distributed.run and --gpus N >= 2")
     k0, k1 = rp.k_shard_bounds(k, world, rank)
     kl = k1 - k0
     g = torch.Generator(device=device).manual_seed(17 + rank)
@@ -407,18 +420,70 @@ def run_row_parallel(args, torch, dist, gk, device, workload, m, k, n, world, ra
         return float(total.item()) / steps
 
     sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", 0)))
-    if rank == 0:
+    if rank == 0 and sample_clocks:
         sampler.start()
-    ms = timed(lambda: rp.gemm_k_sharded(a_codes, a_scales, w_codes, w_scales, ex, out=out, fused=fused),
-               args.steps, max(args.warmup, 3))
-    clocks = sampler.stop() if rank == 0 else None
+    ms = timed(lambda: rp.gemm_k_sharded(a_codes, a_scales, w_codes, w_scales, ex, out=out, fused=fused), steps, warmup)
+    clocks = sampler.stop() if (rank == 0 and sample_clocks) else None
     ms_unfused = timed(lambda: rp.gemm_k_sharded(a_codes, a_scales, w_codes, w_scales, ex, out=out, fused=False),
-                       min(args.steps, 10), 3)
+                       min(steps, 10), 3)
     local = ex.partial(m, n, torch.bfloat16)
-    ms_gemm = timed(lambda: gk.gemm_block_fp8(a_codes, a_scales, w_codes, w_scales, out=local, check=False),
-                    min(args.steps, 10), 3)
+    ms_gemm = timed(lambda: gk.gemm_block_fp8(a_codes, a_scales, w_codes, w_scales, out=local, check=False, status=ex.status),
+                    min(steps, 10), 3)
     timed_out = ex.timed_out()
     ex.close()
+    return {"ms": ms, "unfused_ms": ms_unfused, "gemm_only_ms": ms_gemm, "fused": fused, "timed_out": timed_out,
+            "clocks": clocks, "nvlink_bytes_into_each_gpu": (world - 1) * (m // world) * n * 2}
+
+
+def row_parallel_parity(torch, dist, gk, device, world, rank):
+    """A small K-sharded product on all ranks: fused == unfused bit for bit, and both against the CPU oracle
+    (per-rank partials by oracle.block_fp8_ref, then the restated rank-order sum of oracle.rank_sum_ref)."""
+    from gaudi_kernels_b200 import row_parallel as rp
+    from oracle import block_fp8_ref, fp8_codec_ref, rank_sum_ref
+    m, k, n = 128 * world * 2, 256 * world, 512
+    g = torch.Generator().manual_seed(4321)                                  # every rank builds the same problem
+    x = torch.randn((m, k), generator=g).to(torch.bfloat16)
+    codes_np, scales_np = fp8_codec_ref.quantize_block128((torch.randn((n, k), generator=g) * 0.02).numpy())
+    codes, s = torch.from_numpy(codes_np).view(torch.float8_e4m3fn), torch.from_numpy(scales_np)
+    k0, k1 = rp.k_shard_bounds(k, world, rank)
+    w_dev, s_dev = gk.prepare_weight(codes.to(device), s.to(device), native_half=True)
+    w_loc, s_loc = rp.shard_weight_k(w_dev, s_dev, world, rank)
+    a_codes, a_scales = gk.quantize_act_1x128(x[:, k0:k1].contiguous().to(device), native_half=True)
+    ex = rp.PeerExchange(m * n * 2)
+    fused = rp.gemm_k_sharded(a_codes, a_scales, w_loc, s_loc, ex, fused=True).clone()
+    unfused = rp.gemm_k_sharded(a_codes, a_scales, w_loc, s_loc, ex, fused=False).clone()
+    torch.cuda.synchronize()
+    timed_out = ex.timed_out()
+    ex.close()
+    r0, r1 = rp.row_bounds(m, world, rank)
+    parts64, parts = [], []
+    for r in range(world):
+        a0, a1 = rp.k_shard_bounds(k, world, r)
+        y64, ybf = block_fp8_ref.reference_rows(x[r0:r1, a0:a1].contiguous(), codes[:, a0:a1].contiguous(),
+                                                s[:, a0 // 128:(a1 + 127) // 128].contiguous(), native_half=True)
+        parts64.append(y64)
+        parts.append(ybf)
+    want = rank_sum_ref.rank_sum(torch.stack(parts).reshape(-1).contiguous(), world).view(r1 - r0, n)
+    total64 = sum(parts64)
+    rms = float(total64.pow(2).mean().sqrt())
+    got = fused.cpu()
+    stats = torch.tensor([float((got.double() - total64).abs().max()) / rms,
+                          float((got.double() - want.double()).abs().max()) / rms,
+                          0.0 if torch.equal(fused, unfused) else 1.0, 1.0 if timed_out else 0.0],
+                         dtype=torch.float64, device=device)
+    dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+    st = stats.tolist()
+    return {"shape": "M=%d K=%d N=%d" % (m, k, n), "max_err_over_rms_vs_fp64": st[0],
+            "max_diff_over_rms_vs_oracle_bf16_partials_and_rank_sum": st[1], "fused_equals_unfused_bitwise": st[2] == 0.0,
+            "barrier_wait_expired": st[3] != 0.0, "gate": "1e-2 (bf16 partials: plus one bf16 step per rank)"}
+
+
+def run_row_parallel(args, torch, dist, gk, device, workload, m, k, n, world, rank):
+    if world < 2:
+        raise SystemExit("ffn70b_down is a multi-GPU workload: start it with torch.distributed.run and --gpus N >= 2")
+    res = measure_row_parallel(torch, dist, gk, device, m, k, n, world, rank, args.steps, max(args.warmup, 3))
+    parity = row_parallel_parity(torch, dist, gk, device, world, rank)
+    ms, fused = res["ms"], res["fused"]
     if rank == 0:
         flops = 2.0 * m * k * n
         peak_tflops, peak_how, _ = measured_peaks()
@@ -435,9 +500,10 @@ def run_row_parallel(args, torch, dist, gk, device, workload, m, k, n, world, ra
                              "unit": "TFLOP/s", "frac": flops / world / (ms * 1e-3) / 1e12 / peak_tflops,
                              "peak_source": peak_how + " - of measured", "traffic": None,
                              "kernel": "gemm_block128_kernel<bf16 out> (push mode) + rank_sum_kernel"},
-                "compare": {"unfused_ms_per_step": ms_unfused, "local_gemm_only_ms": ms_gemm,
-                            "nvlink_bytes_into_each_gpu": (world - 1) * (m // world) * n * 2},
-                "clocks": clocks, "gpu_launches": 4 * args.steps, "barrier_wait_expired": timed_out}
+                "compare": {"unfused_ms_per_step": res["unfused_ms"], "local_gemm_only_ms": res["gemm_only_ms"],
+                            "nvlink_bytes_into_each_gpu": res["nvlink_bytes_into_each_gpu"]},
+                "row_parallel_parity": parity,
+                "clocks": res["clocks"], "gpu_launches": 4 * args.steps, "barrier_wait_expired": res["timed_out"]}
         print(json.dumps(line), flush=True)
     dist.destroy_process_group()
 
@@ -476,13 +542,13 @@ def run_reference(args, workload, m, k, n, world, rank):
         block_fp8_ref.reference(x_all[:rows], w, s, native_half=True)
         return time.perf_counter() - t0
 
-    # Size the per-step sample so that the whole run takes about two minutes: a call costs a fixed part (weight
-    # preparation) plus a per-row part, both measured here on two small samples.
+    # Size the per-step sample so that the whole run (warm-up and timed steps alike) takes about two minutes: a
+    # call costs a fixed part (weight preparation) plus a per-row part, both measured here on two small samples.
     r_small, r_big = max(1, args.cpu_rows), min(m, 8 * max(1, args.cpu_rows))
     t_small, t_big = one(r_small), one(r_big)
     per_row = max((t_big - t_small) / max(r_big - r_small, 1), 1e-9)
     fixed = max(t_small - per_row * r_small, 0.0)
-    warmup = min(args.warmup, 1)        # CPU timing needs no long warm-up; keeps the arm within a few minutes
+    warmup = max(args.warmup, 0)
     budget = args.cpu_budget_s / max(args.steps + warmup, 1)
     rows = int(min(m, max(r_small, (budget - fixed) / per_row)))
     rows = max(r_small, rows // 32 * 32 if rows >= 32 else rows)
@@ -492,18 +558,17 @@ def run_reference(args, workload, m, k, n, world, rank):
         dt = one(rows)
         if i >= warmup:
             times.append(dt)
-        if sum(times) > 150.0:          # bounded whatever the host is
-            break
     per_step = sum(times) / len(times)
     value = flops / per_step / 1e12
+    sample = ("%d of the workload's %d activation rows per step (full K and N, weight preparation included); "
+              "the sample is sized so that warm-up and timed steps together take about %.0f s" % (rows, m, args.cpu_budget_s))
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world,
         "steps": len(times), "warmup": warmup, "ms_per_step": per_step * 1e3, "higher_is_better": True,
         "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "f64 (exact E4M3 products)",
         "data": "synthetic",
-        "config": {"workload": "%s M=%d K=%d N=%d" % (workload, m, k, n), "sample": "%d of %d rows" % (rows, m)},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
-                         "sample": "%d activation rows of the workload per step, full K and N, weight preparation included" % rows},
+        "config": make_config(workload, m, k, n, world),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -669,28 +734,101 @@ def main():
     e2e = None
     if not args.no_e2e:
         e2e_steps = args.e2e_steps or min(args.steps, 5)
-        xh = x.pin_memory()
         wh = w_ocp.cpu().pin_memory()
         sh = s_ocp.cpu().pin_memory()
         yh = torch.empty((m, n_local), dtype=torch.bfloat16).pin_memory()
+        if world == 1:
+            xh = x.pin_memory()
+            call = lambda: gk.reference(xh, wh, sh, native_half=True, out=yh)   # returns after the result is on the host
+            call_name = ("gaudi_kernels_b200.reference(x, weight, scales, native_half=True) on pinned host tensors: "
+                         "H2D, re-encode, 1x128 quantize, GEMM, D2H")
+            launches = 1 + 2 * (1 if m < 2048 else min(8, m // 1024))
+        else:
+            from gaudi_kernels_b200 import sharded
+            rows = m // world
+            xh = x[rank * rows:(rank + 1) * rows].contiguous().pin_memory()      # this rank uploads only its rows
+            call = lambda: sharded.reference_sharded(xh, wh, sh, native_half=True, out=yh)
+            call_name = ("gaudi_kernels_b200.sharded.reference_sharded(x rows of this rank, weight slice, scales slice) on "
+                         "pinned host tensors: H2D, re-encode, 1x128 quantize of M / W rows, all-gather of codes and scales "
+                         "(NCCL), GEMM on the rank's columns, D2H of its [M, N / W] slice")
+            launches = 2 + max(1, min(8, m // 2048))
         for _ in range(2):
-            gk.reference(xh, wh, sh, native_half=True, out=yh)
+            call()
         barrier()
         t0 = time.perf_counter()
         for _ in range(e2e_steps):
-            gk.reference(xh, wh, sh, native_half=True, out=yh)   # returns after the result is on the host
+            call()
         torch.cuda.synchronize()
         dt = torch.tensor([time.perf_counter() - t0], dtype=torch.float64, device=device)
         if world > 1:
             dist.all_reduce(dt, op=dist.ReduceOp.MAX)
         e2e_s = float(dt.item()) / e2e_steps
+        h2d = xh.numel() * 2 + wh.numel() + sh.numel() * 4
+        d2h = yh.numel() * 2 + 16
         e2e = {"value": flops_total / e2e_s / 1e12, "unit": UNIT, "ms_per_step": e2e_s * 1e3, "steps": e2e_steps,
-               "h2d_bytes_per_step": xh.numel() * 2 + wh.numel() + sh.numel() * 4,
-               "d2h_bytes_per_step": yh.numel() * 2 + 16,
-               "call": "gaudi_kernels_b200.reference(x, weight, scales, native_half=True) on pinned host tensors: "
-                       "H2D, re-encode, 1x128 quantize, GEMM, D2H",
-               # one weight re-encode, then a 1x128 quantize and a GEMM per pipelined row block
-               "gpu_launches_per_step": 1 + 2 * (1 if m < 2048 else min(8, m // 1024))}
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "call": call_name,
+               "gpu_launches_per_step": launches,
+               "bound": "host link of each GPU: %.1f GB/s to the host, %.1f GB/s from it per rank" % (d2h / e2e_s / 1e9, h2d / e2e_s / 1e9)}
+        if world > 1:
+            e2e["nccl_bytes_into_each_gpu_per_step"] = (world - 1) * (m // world) * (k + 4 * (k // 128))
+            e2e["bytes_are_per_rank"] = True
+
+    # ---- N > 1: parity of rank 0's slice, the same problem on one GPU (strong-scaling reference), row-parallel path
+    multi = {}
+    if world > 1 and not args.no_extras:
+        def guarded(key, fn):
+            try:
+                multi[key] = fn()
+            except Exception as e:  # noqa: BLE001 - a side figure never takes the headline down
+                multi[key + "_error"] = repr(e)[:300]
+
+        def strong():
+            # the unsharded M x K x N product on rank 0's GPU alone, same kernel, same timing rules
+            if rank != 0:
+                return None
+            gg = torch.Generator(device=device).manual_seed(77)
+            wf = torch.randint(0, 0x77, (n, k), generator=gg, device=device, dtype=torch.uint8)
+            sf = torch.rand((n // 128, k // 128), generator=gg, device=device) * 1e-3
+            of = torch.empty((m, n), dtype=torch.bfloat16, device=device)
+            ts = []
+            for i in range(2 + 5):
+                flush.zero_()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                gk.gemm_block_fp8(a_codes, a_scales, wf, sf, out=of, check=False)
+                e1.record()
+                torch.cuda.synchronize()
+                if i >= 2:
+                    ts.append(e0.elapsed_time(e1))
+            t1 = sum(ts) / len(ts)
+            return {"t1_ms": t1, "tN_ms": ms_per_step, "efficiency": t1 / (world * ms_per_step),
+                    "how": "t1 = the unsharded M=%d K=%d N=%d product on rank 0's GPU alone in this run (5 steps, L2 flushed); "
+                           "efficiency = t1 / (N * tN)" % (m, k, n)}
+
+        def parity():
+            if rank != 0:
+                return None
+            from oracle import block_fp8_ref
+            torch.set_num_threads(max(1, os.cpu_count() or 1))
+            rows = 32
+            yb = block_fp8_ref.reference(x[:rows].contiguous(), w_ocp.cpu(), s_ocp.cpu(), native_half=True)
+            got = out[:rows].cpu()
+            return {"rows": rows, "columns": "rank 0's slice [0, %d)" % n_local,
+                    "max_abs_diff_bf16": (got.double() - yb.double()).abs().max().item(),
+                    "rms": float(yb.double().pow(2).mean().sqrt()), "mismatching_elements": int((got != yb).sum())}
+
+        guarded("strong_scaling", strong)
+        guarded("parity_sample", parity)
+        barrier()
+        guarded("row_parallel_parity", lambda: row_parallel_parity(torch, dist, gk, device, world, rank))
+        dm, dk, dn = WORKLOADS["ffn70b_down"]
+        guarded("ffn70b_down", lambda: measure_row_parallel(torch, dist, gk, device, dm, dk, dn, world, rank, 10, 3,
+                                                             sample_clocks=False))
+        if "ffn70b_down" in multi:
+            r = multi["ffn70b_down"]
+            r.pop("clocks", None)
+            r["workload"] = "ffn70b_down M=%d K=%d N=%d, W and A split on K" % (dm, dk, dn)
+            r["tflops_fused"] = 2.0 * dm * dk * dn / (r["ms"] * 1e-3) / 1e12
 
     if rank != 0:
         if world > 1:
@@ -706,10 +844,7 @@ def main():
         "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "e4m3 x e4m3 -> f32 (bf16 out)",
         "data": "synthetic",
-        "config": {"workload": "%s M=%d K=%d N=%d" % (workload, m, k, n),
-                   "sharding": "W rows (N) split over %d ranks, A replicated, output left sharded" % world if world > 1 else "single GPU",
-                   "l2": "256 MiB buffer rewritten between timed steps (L2 is 126 MB); each step timed with its own CUDA events",
-                   "timed": "GEMM on pre-quantized operands resident in HBM"},
+        "config": make_config(workload, m, k, n, world),
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak_tflops, "unit": "TFLOP/s",
                      "frac": achieved / peak_tflops, "peak_source": peak_how + " - of measured",
                      "frac_of_nominal_4500": achieved / 4500.0,
@@ -733,6 +868,7 @@ def main():
             codec = bench_codec(torch, lib, device, 8, 3)
             line["codec_hbm_gbs"] = {k: round(v["gbs"], 1) for k, v in codec.items()}
             line["codec_hbm_frac_of_measured"] = {k: round(v["gbs"] / hbm_gbs, 3) for k, v in codec.items()}
+            line["codec_hbm_frac_of_nominal_8000"] = {k: round(v["gbs"] / 8000.0, 3) for k, v in codec.items()}
 
         def extra_decode():
             for dk, dn in ((4096, 14336), (14336, 4096)):
@@ -750,10 +886,37 @@ def main():
         def extra_checkpoint():
             line["checkpoint_stream_h2d_reencode"] = bench_checkpoint_stream(torch, device)
 
+        def extra_ffn70b():
+            # the multi-GPU workload, unsharded, on this one GPU: the t1 of the strong-scaling curve
+            fm, fk, fn = WORKLOADS["ffn70b"]
+            gg = torch.Generator(device=device).manual_seed(77)
+            af = torch.randint(0, 0x77, (fm, fk), generator=gg, device=device, dtype=torch.uint8)
+            asf = torch.rand((fk // 128, fm), generator=gg, device=device).t()
+            wf = torch.randint(0, 0x77, (fn, fk), generator=gg, device=device, dtype=torch.uint8)
+            sf = torch.rand((fn // 128, fk // 128), generator=gg, device=device) * 1e-3
+            of = torch.empty((fm, fn), dtype=torch.bfloat16, device=device)
+            ts = []
+            for i in range(2 + 5):
+                flush.zero_()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                gk.gemm_block_fp8(af, asf, wf, sf, out=of, check=False)
+                e1.record()
+                torch.cuda.synchronize()
+                if i >= 2:
+                    ts.append(e0.elapsed_time(e1))
+            t1 = sum(ts) / len(ts)
+            line["ffn70b_1gpu"] = {"ms": t1, "tflops": 2.0 * fm * fk * fn / (t1 * 1e-3) / 1e12,
+                                   "workload": "ffn70b M=%d K=%d N=%d unsharded (5 steps, L2 flushed)" % (fm, fk, fn)}
+
+        extra("ffn70b_1gpu", extra_ffn70b)
         extra("codec_hbm_gbs", extra_codec)
         extra("decode_bucket", extra_decode)
         extra("decode_ffn", extra_ffn)
         extra("checkpoint_stream", extra_checkpoint)
+    for key, val in multi.items():
+        if val is not None:
+            line[key] = val
     if gather is not None:
         line["gather"] = gather
     if e2e is not None:

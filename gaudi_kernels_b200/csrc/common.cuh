@@ -1,6 +1,7 @@
 // Shared helpers for the libbfp8 kernels (sm_100a only).
 #pragma once
 
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -26,6 +27,11 @@ inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_
 
 // Number of SMs of the current device (cached per device id).
 int sm_count();
+
+// 2-D row-major tensor map (defined in gemm_tcgen05.cu); box_inner * element size must not exceed the swizzle span.
+int make_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* base, uint64_t inner, uint64_t outer,
+                       uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer,
+                       CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B);
 
 // Raise a kernel's dynamic shared-memory limit once per device (the attribute is per device context).
 template <typename Kernel>

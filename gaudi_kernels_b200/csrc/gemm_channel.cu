@@ -20,8 +20,6 @@
 
 namespace bfp8 {
 
-int make_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* base, uint64_t inner, uint64_t outer,
-                       uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer);
 
 namespace {
 

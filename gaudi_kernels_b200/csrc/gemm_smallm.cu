@@ -455,8 +455,6 @@ int launch_clustered(const CUtensorMap& tmap_w, const CUtensorMap& tmap_a, const
 
 }  // namespace
 
-int make_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* base, uint64_t inner, uint64_t outer,
-                       uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer);
 
 int smallm_padded_rows(int64_t m) { return m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : 128; }
 

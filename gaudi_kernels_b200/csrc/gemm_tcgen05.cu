@@ -432,9 +432,9 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
-// 2-D row-major tensor map with the 128-byte swizzle; box_inner * element size must be <= 128 bytes.
+// 2-D row-major tensor map; box_inner * element size must not exceed the swizzle span (128 bytes by default).
 int make_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* base, uint64_t inner, uint64_t outer,
-                       uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer) {
+                       uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle swizzle) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (fn == nullptr) return BFP8_ERR_CUDA;
   cuuint64_t dims[2] = {inner, outer};
@@ -442,7 +442,7 @@ int make_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* bas
   cuuint32_t box[2] = {box_inner, box_outer};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                  swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     g_last_cuda_error = static_cast<int>(r);
     return BFP8_ERR_CUDA;

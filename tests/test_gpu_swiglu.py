@@ -73,7 +73,9 @@ def test_fused_swiglu_matches_gemm_then_silu_and_mul(gk, m, k, inter, bias, half
     # same accumulation and the same bf16 rounding of both factors: only the last bit of the product may differ
     diff = (got.double() - want.double()).abs()
     assert bool((diff <= _bf16_step(want) + 1e-36).all()), float((diff - _bf16_step(want)).max())
-    assert float((got != want).float().mean()) < 0.02
+    # what is left is the error of ex2.approx inside exp(-g): fewer than 1 product in 10 000 lands on the other side
+    # of a bf16 rounding boundary (measured 5e-7 .. 6e-5 depending on the spread of the gate values)
+    assert float((got != want).float().mean()) < 5e-4
     # end to end against the oracle's GEMM followed by the same step: the GEMM's tolerance (1e-2 of the RMS
     # before rounding, here on each factor) plus the bf16 steps the two roundings can move a product by
     y64, ybf = block_fp8_ref.reference_rows(x, codes, s, native_half=half, bias=b)
@@ -136,7 +138,7 @@ def test_standalone_silu_and_mul_matches_restatement(gk, rows, inter):
     assert torch.equal(torch.isnan(got), torch.isnan(want))
     diff = (got.double() - want.double()).abs()[finite]
     assert bool((diff <= _bf16_step(want)[finite] + 1e-36).all())
-    assert float((got[finite] != want[finite]).float().mean()) < 0.01
+    assert float((got[finite] != want[finite]).float().mean()) < 5e-4 or int((got[finite] != want[finite]).sum()) <= 2
     assert float(got[0, 0]) == 0.0
     # the fused and the stand-alone kernel share the arithmetic: GEMM -> silu_and_mul equals the fused GEMM bit for bit
     if rows == 64:

@@ -42,6 +42,14 @@ def _worker(rank, world, port, out_dir):
         assert torch.equal(local, full[:, start:stop])       # a slice equals the same columns of the full product
         gathered = sharded.gather_columns(local)
         assert torch.equal(gathered, full)
+        # row-sharded quantization + gather of codes and scales (the exchange of reference_sharded) equals
+        # quantizing all rows in one place
+        rows = m // world
+        c_all, s_all = fp8_codec_ref.quantize_act_1x128(x.float().numpy(), native_half=True)          # [M, K], [M, G]
+        c_loc, s_loc_a = fp8_codec_ref.quantize_act_1x128(x[rank * rows:(rank + 1) * rows].float().numpy(), native_half=True)
+        codes_g, scales_g = sharded.gather_quantized_rows(torch.from_numpy(c_loc),
+                                                          torch.from_numpy(np.ascontiguousarray(s_loc_a.T)))
+        assert np.array_equal(codes_g.numpy(), c_all) and np.array_equal(scales_g.numpy(), s_all.T)
         open(os.path.join(out_dir, "ok%d" % rank), "w").write("ok")
     finally:
         dist.destroy_process_group()
