@@ -350,3 +350,4 @@ def test_gemm_ffn70b_rank_slice_row_sample(gk):
     out_view = sharded.gemm_sharded(a_codes, a_scales, wl, sl)
     out_copy = gk.gemm_block_fp8(a_codes, a_scales, wl.contiguous(), sl.contiguous())
     assert torch.equal(out_view, out_copy)
+
