@@ -467,15 +467,19 @@ def row_parallel_parity(torch, dist, gk, device, world, rank):
     total64 = sum(parts64)
     rms = float(total64.pow(2).mean().sqrt())
     got = fused.cpu()
+    # the gate of tests/test_gpu_row_parallel.py: the GEMM tolerance per rank plus one bf16 step per rounding
+    bound = 1e-2 * rms * world + (world + 1) * 2.0 ** -7 * float(total64.abs().max())
+    gate_ok = (float((got.double() - total64).abs().max()) <= bound and float((got.double() - want.double()).abs().max()) <= bound)
     stats = torch.tensor([float((got.double() - total64).abs().max()) / rms,
                           float((got.double() - want.double()).abs().max()) / rms,
-                          0.0 if torch.equal(fused, unfused) else 1.0, 1.0 if timed_out else 0.0],
+                          0.0 if torch.equal(fused, unfused) else 1.0, 1.0 if timed_out else 0.0, 0.0 if gate_ok else 1.0],
                          dtype=torch.float64, device=device)
     dist.all_reduce(stats, op=dist.ReduceOp.MAX)
     st = stats.tolist()
     return {"shape": "M=%d K=%d N=%d" % (m, k, n), "max_err_over_rms_vs_fp64": st[0],
             "max_diff_over_rms_vs_oracle_bf16_partials_and_rank_sum": st[1], "fused_equals_unfused_bitwise": st[2] == 0.0,
-            "barrier_wait_expired": st[3] != 0.0, "gate": "1e-2 (bf16 partials: plus one bf16 step per rank)"}
+            "barrier_wait_expired": st[3] != 0.0, "within_gate_on_every_rank": st[4] == 0.0,
+            "gate": "1e-2 of the RMS per rank plus one bf16 step per rounding (W + 1 roundings), as tests/test_gpu_row_parallel.py"}
 
 
 def run_row_parallel(args, torch, dist, gk, device, workload, m, k, n, world, rank):
