@@ -333,22 +333,43 @@ def bench_decode_ffn(torch, lib, device, hidden=4096, inter=14336, reps=10, roun
                                               y.data_ptr(), 1, hidden, m, hidden, inter, ws.data_ptr(), ws_bytes, sp, st))
                 assert rcs == (0, 0, 0, 0, 0), rcs
 
-        ffn(2)
-        torch.cuda.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            ffn(reps)
-        ts = []
-        for _ in range(rounds):
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            graph.replay()
-            e1.record()
+        h = torch.empty((m, inter), dtype=torch.bfloat16, device=device)
+
+        def ffn_fused(count):
+            # the same step on the interleaved gate/up weight (the copy the prefill kernel reads): one GEMM whose
+            # epilogue applies SwiGLU, then the plain 1x128 quantizer - four kernels, no [M, 2 I] round trip
+            st = torch.cuda.current_stream().cuda_stream
+            for i in range(count):
+                wgu, sgu, wd, sd = sets[i % 2]
+                rcs = (lib.bfp8_quant_act_1x128_bf16(x.data_ptr(), m, hidden, hidden, a1.data_ptr(), hidden, s1.data_ptr(), 1, m, 1, None, st),
+                       lib.bfp8_gemm_block128_swiglu(a1.data_ptr(), hidden, s1.data_ptr(), m, wgu.data_ptr(), hidden, sgu.data_ptr(), None,
+                                                     h.data_ptr(), inter, m, inter, hidden, ws.data_ptr(), ws_bytes, sp, st),
+                       lib.bfp8_quant_act_1x128_bf16(h.data_ptr(), m, inter, inter, a2.data_ptr(), inter, s2.data_ptr(), 1, m, 1, None, st),
+                       lib.bfp8_gemm_block128(a2.data_ptr(), inter, s2.data_ptr(), m, wd.data_ptr(), inter, sd.data_ptr(), None,
+                                              y.data_ptr(), 1, hidden, m, hidden, inter, ws.data_ptr(), ws_bytes, sp, st))
+                assert rcs == (0, 0, 0, 0), rcs
+
+        def timed_graph(fn):
+            fn(2)
             torch.cuda.synchronize()
-            ts.append(e0.elapsed_time(e1) / reps)
-        us = statistics.median(ts) * 1e3
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                fn(reps)
+            ts = []
+            for _ in range(rounds):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                graph.replay()
+                e1.record()
+                torch.cuda.synchronize()
+                ts.append(e0.elapsed_time(e1) / reps)
+            return statistics.median(ts) * 1e3
+
+        us = timed_graph(ffn)
+        us_fused = timed_graph(ffn_fused)
         nbytes = 3 * inter * hidden                                  # weight codes; everything else is below 1 %
-        out["M=%d" % m] = {"us": round(us, 2), "weight_gbs": round(nbytes / us / 1e3, 1), "kernels": 5}
+        out["M=%d" % m] = {"us": round(us, 2), "weight_gbs": round(nbytes / us / 1e3, 1), "kernels": 5,
+                           "us_fused_swiglu_gemm_4_kernels": round(us_fused, 2)}
     assert int(status.cpu()[2]) == 0
     return out
 

@@ -51,7 +51,7 @@ SIGNATURES = {
     "bfp8_peer_barrier": (_int, [_ptr, _int, _int, _c.c_uint32, _i64, _ptr, _ptr]),
     "bfp8_swiglu_interleave_weight": (_int, [_ptr, _i64, _ptr, _i64, _i64, _i64, _ptr]),
     "bfp8_gemm_block128_swiglu": (_int, [_ptr, _i64, _ptr, _i64, _ptr, _i64, _ptr, _ptr, _ptr, _i64,
-                                         _i64, _i64, _i64, _ptr, _ptr]),
+                                         _i64, _i64, _i64, _ptr, _sz, _ptr, _ptr]),
 }
 
 _lib = None

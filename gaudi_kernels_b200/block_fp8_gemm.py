@@ -239,12 +239,14 @@ def prepare_weight_swiglu(weight, scales, native_half=True):
     return dst.view(torch.float8_e4m3fn), scales
 
 
-def gemm_block_fp8_swiglu(a_codes, a_scales, w_codes, w_scales, bias=None, out=None, check=True):
+def gemm_block_fp8_swiglu(a_codes, a_scales, w_codes, w_scales, bias=None, out=None, check=True, small_m=True):
     """bf16 [M, I] = silu(gate) * up, with gate | up = the block-scaled GEMM of gemm_block_fp8 rounded to bf16.
 
     The gate/up GEMM and gk_silu_and_mul_bf16_v1 (csrc/tpc/generic_dense/silu_and_mul_bf16.c:16) as one
     kernel.  w_codes [2 * I, K'] and w_scales [2 * I / 128, G] come from prepare_weight_swiglu (K' is K
-    rounded up to 16); bias fp32 [2 * I] in the fused weight's original order, or None.
+    rounded up to 16); bias fp32 [2 * I] in the fused weight's original order, or None.  With M <= 128 the
+    weight-streaming (decode bucket) schedule runs on the same interleaved weight; small_m=False keeps the
+    large-tile schedule for every M.
     """
     for name, t in (("a_codes", a_codes), ("w_codes", w_codes)):
         if (not isinstance(t, torch.Tensor) or t.dtype not in (torch.float8_e4m3fn, torch.uint8) or t.ndim != 2
@@ -275,12 +277,16 @@ def gemm_block_fp8_swiglu(a_codes, a_scales, w_codes, w_scales, bias=None, out=N
         elif (out.dtype != torch.bfloat16 or tuple(out.shape) != (m, inter) or out.stride(1) != 1 or out.device != dev):
             raise ValueError("out must be bf16 [M, I] with unit column stride on the operand device")
         st = _status_buffer(dev)
+        ws_bytes = lib.bfp8_gemm_block128_workspace_bytes(m, n2, w_codes.shape[1]) if (small_m and m <= 128) else 0
+        ws = _workspace(dev, ws_bytes) if ws_bytes else None
         rc = lib.bfp8_gemm_block128_swiglu(
             a_codes.data_ptr(), a_codes.stride(0), sa.data_ptr(), ldsa, w_codes.data_ptr(), w_codes.stride(0),
             w_scales.data_ptr(), bias.data_ptr() if bias is not None else None, out.data_ptr(), out.stride(0),
-            m, inter, w_codes.shape[1], st.data_ptr() + 8, _stream_ptr())
+            m, inter, w_codes.shape[1], ws.data_ptr() if ws is not None else None, ws_bytes, st.data_ptr() + 8,
+            _stream_ptr())
         _lib.check(rc, "bfp8_gemm_block128_swiglu")
         if check and _read_status(st)[1] & _lib.STATUS_WAIT_TIMEOUT:
+            _workspaces.clear()
             raise _lib.Bfp8Error(_WAIT_TIMEOUT_MSG)
     return out
 

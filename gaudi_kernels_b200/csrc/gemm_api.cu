@@ -18,7 +18,7 @@ int launch_gemm_pair(const uint8_t* a_codes, int64_t lda, const float* a_scales,
 int launch_gemm_smallm(const uint8_t* a_codes, int64_t lda, const float* a_scales, int64_t ldsa,
                        const uint8_t* w_codes, int64_t ldw, const float* w_scales, const float* bias, void* out,
                        int out_dtype, int64_t ldo, int64_t m, int64_t n, int64_t k, void* workspace,
-                       uint32_t* status_dev, long long wait_limit, int max_ctas, cudaStream_t st);
+                       uint32_t* status_dev, long long wait_limit, int max_ctas, int inter, cudaStream_t st);
 int launch_gemm_channel(const uint8_t* a_codes, int64_t lda, const float* a_scales, const uint8_t* w_codes,
                         int64_t ldw, const float* w_scales, const float* bias, void* out, int out_dtype, int64_t ldo,
                         int64_t m, int64_t n, int64_t k, uint32_t* status_dev, long long wait_limit, int max_ctas,
@@ -69,7 +69,7 @@ extern "C" int bfp8_gemm_block128_ex(const uint8_t* a_codes, int64_t lda, const 
     if (!aligned(workspace, 256)) return BFP8_ERR_ALIGN;
     if (sm_count() > kMaxCtas) return BFP8_ERR_UNSUPPORTED;
     return launch_gemm_smallm(a_codes, lda, a_scales, ldsa, w_codes, ldw, w_scales, bias, out, out_dtype, ldo,
-                              m, n, k, workspace, status_dev, limit, max_ctas, st);
+                              m, n, k, workspace, status_dev, limit, max_ctas, /*inter=*/0, st);
   }
   if (schedule == 3)
     return launch_gemm_pair(a_codes, lda, a_scales, ldsa, w_codes, ldw, w_scales, bias, out, out_dtype, ldo, m, n, k,
@@ -146,7 +146,8 @@ extern "C" int bfp8_swiglu_interleave_weight(const uint8_t* w_codes, int64_t ld_
 extern "C" int bfp8_gemm_block128_swiglu(const uint8_t* a_codes, int64_t lda, const float* a_scales, int64_t ldsa,
                                          const uint8_t* w_codes, int64_t ldw, const float* w_scales,
                                          const float* bias, void* out, int64_t ldo,
-                                         int64_t m, int64_t inter, int64_t k, uint32_t* status_dev, void* stream) {
+                                         int64_t m, int64_t inter, int64_t k,
+                                         void* workspace, size_t workspace_bytes, uint32_t* status_dev, void* stream) {
   if (!a_codes || !a_scales || !w_codes || !w_scales || !out || !status_dev) return BFP8_ERR_NULL;
   if (m <= 0 || inter <= 0 || k <= 0 || m > (1 << 30) || inter > (1 << 29) || k > (1 << 30)) return BFP8_ERR_SHAPE;
   if (lda < k || ldw < k || ldo < inter || ldsa < m) return BFP8_ERR_SHAPE;
@@ -155,6 +156,15 @@ extern "C" int bfp8_gemm_block128_swiglu(const uint8_t* a_codes, int64_t lda, co
   if (!aligned(a_scales, 4) || !aligned(w_scales, 4) || !aligned(status_dev, 4)) return BFP8_ERR_ALIGN;
   if (bias && !aligned(bias, 4)) return BFP8_ERR_ALIGN;
   if (!aligned(out, 16) || ldo % 8 != 0) return BFP8_ERR_ALIGN;
+  // decode bucket: the weight-streaming schedule, when the caller brought its scratch
+  if (m <= kSmallMRows && smallm_supported(2 * inter) && workspace != nullptr) {
+    if (workspace_bytes < bfp8_gemm_block128_workspace_bytes(m, 2 * inter, k)) return BFP8_ERR_WORKSPACE;
+    if (!aligned(workspace, 256)) return BFP8_ERR_ALIGN;
+    if (sm_count() > kMaxCtas) return BFP8_ERR_UNSUPPORTED;
+    return launch_gemm_smallm(a_codes, lda, a_scales, ldsa, w_codes, ldw, w_scales, bias, out, BFP8_OUT_BF16, ldo, m,
+                              2 * inter, k, workspace, status_dev, kDefaultWaitLimit, 0, static_cast<int>(inter),
+                              static_cast<cudaStream_t>(stream));
+  }
   return launch_gemm_large(a_codes, lda, a_scales, ldsa, w_codes, ldw, w_scales, bias, out, BFP8_OUT_BF16, ldo,
                            m, 2 * inter, k, status_dev, kDefaultWaitLimit, 0, /*band=*/0, static_cast<int>(inter),
                            /*push=*/nullptr, static_cast<cudaStream_t>(stream));

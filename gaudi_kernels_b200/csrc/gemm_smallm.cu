@@ -26,6 +26,14 @@
 // warp 6 scale loader: it fetches the scale products of the units ahead
 // (global-memory latency is far longer than a unit's 16 KB of HBM time) and parks them in a small
 // shared-memory ring next to the TMEM buffers.  All barrier waits are bounded.
+//
+// SwiGLU form (Params::inter > 0): W is a fused gate/up weight whose rows were interleaved in chunks of 64
+// (bfp8_swiglu_interleave_weight - the layout the large-tile fused kernel reads, so prefill and decode share one
+// copy), so a 128-row tile holds the gate rows (TMEM lanes 0-63) and the up rows (lanes 64-127) of the same 64
+// outputs.  The two halves take their weight scale from the gate and from the up block of the original scale
+// grid (two scale vectors per unit), both factors get their bias and are rounded to bf16 as the unfused GEMM
+// would store them, the up half hands its values to the gate half through shared memory, and the gate half
+// stores bf16(silu(gate) * up) - csrc/tpc/generic_dense/silu_and_mul_bf16.c:16 - into the [M, inter] output.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -44,6 +52,8 @@ constexpr int kAccBufs = 4;
 constexpr int kWBytes = BN * BK;   // 16 KB of W per unit
 constexpr int kMaxStages = 10;
 constexpr int kSmemBudget = 200 * 1024;
+constexpr int kSwigluRows = 16;    // activation rows per exchange round of the SwiGLU form
+constexpr int kSwigluExBytes = kSwigluRows * 64 * 4;
 
 template <int MP>
 struct Cfg {
@@ -61,6 +71,7 @@ struct SmemTail {
   uint64_t tmem_empty[kAccBufs];
   uint64_t scale_full[kAccBufs];
   float scale[kAccBufs][128];        // sa[g, 0..MP) * sw[tile, g] of the unit in each TMEM buffer
+  float scale_up[kAccBufs][128];     // SwiGLU form: the same with the up block's weight scale (lanes 64-127)
   uint32_t tmem_base;
   uint32_t abort_flag;
   uint32_t last_flag;
@@ -80,7 +91,38 @@ struct Params {
   long long wait_limit;
   uint32_t* status;
   int cluster;             // CTAs per tile when the kernel runs as clusters (kCluster), else unused
+  int inter;               // SwiGLU form: width of the gate and of the up projection (n = 2 * inter), else 0
 };
+
+// SwiGLU form: the up half of a tile (weight rows 64..127) hands bf16(up) to the gate half through `ex`
+// ([kRows][64] floats in shared memory); all 128 epilogue threads call this together (two named barriers inside).
+// `v[j]` is the thread's fp32 sum for activation row j0 + j (bias not yet added), `rows` how many are valid.
+template <int kRows>
+__device__ __forceinline__ void swiglu_finish(const Params& p, float* ex, int tile, int wrow, const float* v,
+                                              int j0, int rows, bool write) {
+  const bool gate = wrow < 64;
+  const int o = gate ? wrow : wrow - 64;                       // output column inside the tile's 64
+  const int col = tile * 64 + o;
+  float b = 0.0f;
+  if (p.bias != nullptr) b = __ldg(p.bias + (gate ? col : p.inter + col));
+  if (!gate) {
+#pragma unroll
+    for (int j = 0; j < kRows; ++j)
+      if (j < rows) ex[j * 64 + o] = bf16_bits_to_float(float_to_bf16_bits(v[j] + b));
+  }
+  asm volatile("bar.sync 1, 128;" ::: "memory");
+  if (gate && write) {
+    uint16_t* out = reinterpret_cast<uint16_t*>(p.out) + col;
+#pragma unroll
+    for (int j = 0; j < kRows; ++j) {
+      if (j < rows && j0 + j < p.m) {
+        const float g = bf16_bits_to_float(float_to_bf16_bits(v[j] + b));
+        out[static_cast<int64_t>(j0 + j) * p.ldo] = static_cast<uint16_t>(float_to_bf16_bits(silu_mul(g, ex[j * 64 + o])));
+      }
+    }
+  }
+  asm volatile("bar.sync 1, 128;" ::: "memory");             // `ex` may be rewritten
+}
 
 // First unit of CTA c when `total` units are split over `parts` CTAs.
 __host__ __device__ inline long long first_unit(long long c, long long total, long long parts) {
@@ -91,7 +133,7 @@ __host__ __device__ inline int cta_of_unit(long long u, long long total, long lo
   return static_cast<int>(((u + 1) * parts - 1) / total);
 }
 
-template <int MP, bool kCluster>
+template <int MP, bool kCluster, bool kSwiGLU>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a,
                    const Params p) {
@@ -100,6 +142,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
   SmemTail* tail = reinterpret_cast<SmemTail*>(smem + C::kStages * C::kStageBytes);
+  float* swiglu_ex = reinterpret_cast<float*>(tail + 1);       // [kSwigluRows][64], SwiGLU form only
   volatile uint32_t* abort_flag = &tail->abort_flag;
 
   const int warp = threadIdx.x >> 5;
@@ -191,12 +234,16 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     constexpr int kPer = (MP + 31) / 32;                         // activation scales per lane and unit
     // Raw scales of the next kScaleAhead units.  They are multiplied only when their unit comes up: using a
     // loaded value right away would stall this warp for a full L2 round trip on every unit.
-    float va[kScaleAhead][kPer], vw[kScaleAhead];
+    float va[kScaleAhead][kPer], vw[kScaleAhead], vu[kSwiGLU ? kScaleAhead : 1];
+    constexpr bool swiglu = kSwiGLU;
     int f_tile = static_cast<int>(u0 / G), f_g = static_cast<int>(u0 % G);   // unit the next fetch belongs to
-    auto fetch = [&](float (&dst)[kPer], float& sw) {
+    auto fetch = [&](float (&dst)[kPer], float& sw, float& su) {
       const int tile = f_tile, g = f_g;
       if (++f_g == G) { f_g = 0; ++f_tile; }
-      sw = __ldg(p.w_scales + static_cast<int64_t>(tile) * G + g);
+      // SwiGLU form: tile t holds outputs 64 t .. 64 t + 63, i.e. scale block t / 2 of the gate rows and of the up rows
+      const int nb = swiglu ? (tile >> 1) : tile;
+      sw = __ldg(p.w_scales + static_cast<int64_t>(nb) * G + g);
+      su = swiglu ? __ldg(p.w_scales + static_cast<int64_t>((p.inter >> 7) + nb) * G + g) : 0.0f;
       const float* sa = p.a_scales + static_cast<int64_t>(g) * p.ldsa;
 #pragma unroll
       for (int q = 0; q < kPer; ++q) {
@@ -206,7 +253,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     };
 #pragma unroll
     for (int i = 0; i < kScaleAhead; ++i)
-      if (u0 + i < u1) fetch(va[i], vw[i]);
+      if (u0 + i < u1) fetch(va[i], vw[i], vu[kSwiGLU ? i : 0]);
     uint32_t kb = 0;
     bool ok = true;
     for (long long base = u0; base < u1 && ok; base += kScaleAhead) {
@@ -221,10 +268,13 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
           if (ok) {
 #pragma unroll
             for (int q = 0; q < kPer; ++q)
-              if (lane + 32 * q < MP) tail->scale[buf][lane + 32 * q] = va[i][q] * vw[i];
+              if (lane + 32 * q < MP) {
+                tail->scale[buf][lane + 32 * q] = va[i][q] * vw[i];
+                if (swiglu) tail->scale_up[buf][lane + 32 * q] = va[i][q] * vu[kSwiGLU ? i : 0];
+              }
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&tail->scale_full[buf]));
-            if (u + kScaleAhead < u1) fetch(va[i], vw[i]);
+            if (u + kScaleAhead < u1) fetch(va[i], vw[i], vu[kSwiGLU ? i : 0]);
             ++kb;
           }
         }
@@ -235,6 +285,8 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     const int wrow = warp * 32 + lane;                         // weight row inside the tile = TMEM lane
     const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
     const int epi_tid = threadIdx.x;                           // 0..127
+    // SwiGLU form: the up rows (lanes 64-127) use the up block's scale products
+    const float* my_scale = (kSwiGLU && wrow >= 64) ? &tail->scale_up[0][0] : &tail->scale[0][0];
     float acc[MP];
 #pragma unroll
     for (int j = 0; j < MP; ++j) acc[j] = 0.0f;
@@ -242,48 +294,11 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     long long seg_start = u0;
     bool ok = true;
     int tile = static_cast<int>(u0 / G), g = static_cast<int>(u0 % G) - 1;
-    // A thread whose bounded wait expired does not leave the loop in the plain form: the four epilogue warps meet
-    // at named barriers at every segment end, so it keeps walking the units (without waiting or touching TMEM)
-    // and takes part in those barriers; its siblings see the abort flag at their next wait and do the same.
-    for (long long u = u0; u < u1 && (ok || !kCluster); ++u, ++kb) {
-      if (++g == G) { g = 0; ++tile; }
-      const uint32_t buf = kb % kAccBufs, acc_phase = (kb / kAccBufs) & 1u;
-      if (ok) {
-        // uniform across the warp before the warp-collective TMEM loads
-        ok = __all_sync(0xffffffffu,
-                        ptx::mbar_wait(ptx::smem_u32(&tail->tmem_full[buf]), acc_phase, abort_flag, p.wait_limit) &&
-                        ptx::mbar_wait(ptx::smem_u32(&tail->scale_full[buf]), acc_phase, abort_flag, p.wait_limit));
-      }
-      if (ok) {
-      ptx::tc_fence_after_sync();
-      const uint32_t taddr = tmem_base + lane_addr + buf * MP;
-      constexpr int kChunk = MP < 64 ? MP : 64;                  // columns fetched per TMEM round trip
-#pragma unroll
-      for (int h = 0; h < MP / kChunk; ++h) {
-        uint32_t r[kChunk / 16][16];
-#pragma unroll
-        for (int c = 0; c < kChunk / 16; ++c) ptx::tmem_ld16(taddr + h * kChunk + c * 16, r[c]);
-        float s[kChunk];
-#pragma unroll
-        for (int j = 0; j < kChunk; j += 4) {
-          const float4 t4 = *reinterpret_cast<const float4*>(&tail->scale[buf][h * kChunk + j]);
-          s[j] = t4.x; s[j + 1] = t4.y; s[j + 2] = t4.z; s[j + 3] = t4.w;
-        }
-        ptx::tmem_wait_ld16(r[0]);
-#pragma unroll
-        for (int c = 1; c < kChunk / 16; ++c) ptx::tmem_regs_ready16(r[c]);
-#pragma unroll
-        for (int c = 0; c < kChunk / 16; ++c)
-#pragma unroll
-          for (int j = 0; j < 16; ++j)
-            acc[h * kChunk + c * 16 + j] = fmaf(__uint_as_float(r[c][j]), s[c * 16 + j], acc[h * kChunk + c * 16 + j]);
-      }
-      ptx::tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&tail->tmem_empty[buf]));
-      }
-
-      if (!kCluster && (g == G - 1 || u == u1 - 1)) {
+    // End of this CTA's segment of a tile (plain form).  The four epilogue warps meet at named barriers here, so a
+    // thread whose bounded wait expired still calls this for every remaining segment end (alive == false: it takes
+    // part in the barriers and the counter protocol, stores nothing), see the loop after the main one.
+    long long u = u0;
+    auto segment_end = [&](bool alive) {
         // ---- end of this CTA's segment of the tile
         const long long tile_first = static_cast<long long>(tile) * G;
         const int c_first = cta_of_unit(tile_first, p.total_units, parts);
@@ -321,7 +336,14 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
           }
           asm volatile("bar.sync 1, 128;" ::: "memory");          // last_flag may be rewritten next segment
         }
-        if (do_store && ok && col < p.n) {
+        if (kSwiGLU) {
+          // SwiGLU form: do_store is the same for all 128 threads, so the barriers inside are safe
+          if (do_store) {
+#pragma unroll
+            for (int j0 = 0; j0 < MP; j0 += kSwigluRows)
+              swiglu_finish<kSwigluRows>(p, swiglu_ex, tile, wrow, acc + j0, j0, kSwigluRows, alive);
+          }
+        } else if (do_store && alive && col < p.n) {
           const float b = p.bias != nullptr ? __ldg(p.bias + col) : 0.0f;
           if (p.out_bf16) {
             uint16_t* o = reinterpret_cast<uint16_t*>(p.out) + col;
@@ -338,6 +360,49 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
 #pragma unroll
         for (int j = 0; j < MP; ++j) acc[j] = 0.0f;
         seg_start = u + 1;
+    };
+    for (; u < u1; ++u, ++kb) {
+      if (++g == G) { g = 0; ++tile; }
+      const uint32_t buf = kb % kAccBufs, acc_phase = (kb / kAccBufs) & 1u;
+      // uniform across the warp before the warp-collective TMEM loads
+      ok = __all_sync(0xffffffffu,
+                      ptx::mbar_wait(ptx::smem_u32(&tail->tmem_full[buf]), acc_phase, abort_flag, p.wait_limit) &&
+                      ptx::mbar_wait(ptx::smem_u32(&tail->scale_full[buf]), acc_phase, abort_flag, p.wait_limit));
+      if (!ok) break;
+      ptx::tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + lane_addr + buf * MP;
+      constexpr int kChunk = MP < 64 ? MP : 64;                  // columns fetched per TMEM round trip
+#pragma unroll
+      for (int h = 0; h < MP / kChunk; ++h) {
+        uint32_t r[kChunk / 16][16];
+#pragma unroll
+        for (int c = 0; c < kChunk / 16; ++c) ptx::tmem_ld16(taddr + h * kChunk + c * 16, r[c]);
+        float s[kChunk];
+#pragma unroll
+        for (int j = 0; j < kChunk; j += 4) {
+          const float4 t4 = *reinterpret_cast<const float4*>(&my_scale[buf * 128 + h * kChunk + j]);
+          s[j] = t4.x; s[j + 1] = t4.y; s[j + 2] = t4.z; s[j + 3] = t4.w;
+        }
+        ptx::tmem_wait_ld16(r[0]);
+#pragma unroll
+        for (int c = 1; c < kChunk / 16; ++c) ptx::tmem_regs_ready16(r[c]);
+#pragma unroll
+        for (int c = 0; c < kChunk / 16; ++c)
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            acc[h * kChunk + c * 16 + j] = fmaf(__uint_as_float(r[c][j]), s[c * 16 + j], acc[h * kChunk + c * 16 + j]);
+      }
+      ptx::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&tail->tmem_empty[buf]));
+      if (!kCluster && (g == G - 1 || u == u1 - 1)) segment_end(true);
+    }
+    if (!kCluster && !ok) {
+      // this thread gave up inside unit u (g and tile already stand at that unit): walk the rest of the list and
+      // keep every appointment at the segment ends; the siblings see the abort flag at their next wait and follow
+      for (bool first = true; u < u1; ++u, first = false) {
+        if (!first && ++g == G) { g = 0; ++tile; }
+        if (g == G - 1 || u == u1 - 1) segment_end(false);
       }
     }
     if (kCluster) {
@@ -359,7 +424,22 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
       // #2: all partials have arrived
       ptx::cluster_sync_all();
       const int col = static_cast<int>(ctile) * BN + wrow;
-      if (ok && col < p.n) {
+      if (kSwiGLU) {
+        // SwiGLU form: this CTA's rows in rounds of kSwigluRows; every epilogue thread takes part in the barriers
+        const float* mine = reinterpret_cast<const float*>(smem);
+        for (int jj0 = 0; jj0 < rows_per; jj0 += kSwigluRows) {
+          float v[kSwigluRows];
+#pragma unroll
+          for (int q = 0; q < kSwigluRows; ++q) {
+            float sum = 0.0f;
+            if (jj0 + q < rows_per)
+              for (int r = 0; r < cs; ++r) sum += mine[(r * rows_per + jj0 + q) * BN + wrow];   // rank order = K order
+            v[q] = sum;
+          }
+          swiglu_finish<kSwigluRows>(p, swiglu_ex, static_cast<int>(ctile), wrow, v, crank * rows_per + jj0,
+                                     min(kSwigluRows, rows_per - jj0), ok);
+        }
+      } else if (ok && col < p.n) {
         const float b = p.bias != nullptr ? __ldg(p.bias + col) : 0.0f;
         const float* mine = reinterpret_cast<const float*>(smem);
         for (int jj = 0; jj < rows_per; ++jj) {
@@ -391,12 +471,12 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   if (threadIdx.x == 0 && tail->abort_flag != 0) atomicOr(p.status, BFP8_STATUS_WAIT_TIMEOUT);
 }
 
-template <int MP>
+template <int MP, bool kSwiGLU>
 int launch(const CUtensorMap& tmap_w, const CUtensorMap& tmap_a, const Params& p, int grid, cudaStream_t st) {
   using C = Cfg<MP>;
-  constexpr int smem = 1024 + C::kStages * C::kStageBytes + sizeof(SmemTail);
+  constexpr int smem = 1024 + C::kStages * C::kStageBytes + sizeof(SmemTail) + kSwigluExBytes;
   static bool done[64] = {};
-  const int rc = ensure_smem_limit(gemm_smallm_kernel<MP, false>, smem, done);
+  const int rc = ensure_smem_limit(gemm_smallm_kernel<MP, false, kSwiGLU>, smem, done);
   if (rc != BFP8_OK) return rc;
   // launched so that the set-up of this kernel may overlap the tail of the previous kernel in the stream
   cudaLaunchConfig_t cfg = {};
@@ -409,19 +489,19 @@ int launch(const CUtensorMap& tmap_w, const CUtensorMap& tmap_a, const Params& p
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  BFP8_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_smallm_kernel<MP, false>, tmap_w, tmap_a, p));
+  BFP8_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_smallm_kernel<MP, false, kSwiGLU>, tmap_w, tmap_a, p));
   return BFP8_OK;
 }
 
 // Cluster form: p.tiles clusters of p.cluster CTAs.  Returns BFP8_ERR_UNSUPPORTED without launching when the
 // device cannot hold all clusters at once (the caller then uses the plain form).
-template <int MP>
+template <int MP, bool kSwiGLU>
 int launch_clustered(const CUtensorMap& tmap_w, const CUtensorMap& tmap_a, const Params& p, cudaStream_t st) {
   using C = Cfg<MP>;
-  constexpr int smem = 1024 + C::kStages * C::kStageBytes + sizeof(SmemTail);
+  constexpr int smem = 1024 + C::kStages * C::kStageBytes + sizeof(SmemTail) + kSwigluExBytes;
   static_assert(MP * BN * 4 <= C::kStages * C::kStageBytes, "the exchange area reuses the pipeline buffers");
   static bool done[64] = {};
-  const int rc = ensure_smem_limit(gemm_smallm_kernel<MP, true>, smem, done);
+  const int rc = ensure_smem_limit(gemm_smallm_kernel<MP, true, kSwiGLU>, smem, done);
   if (rc != BFP8_OK) return rc;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(p.tiles * p.cluster), 1, 1);
@@ -444,17 +524,39 @@ int launch_clustered(const CUtensorMap& tmap_w, const CUtensorMap& tmap_a, const
   const int slot = p.cluster == 2 ? 0 : p.cluster == 4 ? 1 : 2;
   int cap = (dev >= 0 && dev < 64) ? max_clusters[dev][slot] : 0;
   if (cap == 0) {
-    BFP8_CUDA_TRY(cudaOccupancyMaxActiveClusters(&cap, gemm_smallm_kernel<MP, true>, &cfg));
+    BFP8_CUDA_TRY(cudaOccupancyMaxActiveClusters(&cap, gemm_smallm_kernel<MP, true, kSwiGLU>, &cfg));
     if (cap <= 0) cap = -1;
     if (dev >= 0 && dev < 64) max_clusters[dev][slot] = cap;
   }
   if (cap < p.tiles) return BFP8_ERR_UNSUPPORTED;
-  BFP8_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_smallm_kernel<MP, true>, tmap_w, tmap_a, p));
+  BFP8_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_smallm_kernel<MP, true, kSwiGLU>, tmap_w, tmap_a, p));
   return BFP8_OK;
 }
 
 }  // namespace
 
+
+// Cluster form where it applies (and the device can hold all clusters at once), else the plain form.
+template <bool kSwiGLU>
+int dispatch(int mp, const CUtensorMap& tmap_w, const CUtensorMap& tmap_a, Params& p, int grid, cudaStream_t st) {
+  if (p.cluster >= 2) {
+    int crc;
+    switch (mp) {
+      case 16: crc = launch_clustered<16, kSwiGLU>(tmap_w, tmap_a, p, st); break;
+      case 32: crc = launch_clustered<32, kSwiGLU>(tmap_w, tmap_a, p, st); break;
+      case 64: crc = launch_clustered<64, kSwiGLU>(tmap_w, tmap_a, p, st); break;
+      default: crc = launch_clustered<128, kSwiGLU>(tmap_w, tmap_a, p, st); break;
+    }
+    if (crc != BFP8_ERR_UNSUPPORTED) return crc;
+    p.cluster = 0;
+  }
+  switch (mp) {
+    case 16: return launch<16, kSwiGLU>(tmap_w, tmap_a, p, grid, st);
+    case 32: return launch<32, kSwiGLU>(tmap_w, tmap_a, p, grid, st);
+    case 64: return launch<64, kSwiGLU>(tmap_w, tmap_a, p, grid, st);
+    default: return launch<128, kSwiGLU>(tmap_w, tmap_a, p, grid, st);
+  }
+}
 
 int smallm_padded_rows(int64_t m) { return m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : 128; }
 
@@ -498,7 +600,8 @@ int smallm_cluster_size(int64_t tiles, int64_t groups, int sms) {
 int launch_gemm_smallm(const uint8_t* a_codes, int64_t lda, const float* a_scales, int64_t ldsa,
                        const uint8_t* w_codes, int64_t ldw, const float* w_scales, const float* bias, void* out,
                        int out_dtype, int64_t ldo, int64_t m, int64_t n, int64_t k, void* workspace,
-                       uint32_t* status_dev, long long wait_limit, int max_ctas, cudaStream_t st) {
+                       uint32_t* status_dev, long long wait_limit, int max_ctas, int inter, cudaStream_t st) {
+  // inter > 0 selects the SwiGLU form: W has n = 2 * inter interleaved rows, `out` is bf16 [m, inter]
   // max_ctas > 0 (a caller-imposed CTA limit, used by tests and by the entry point with the built-in scratch)
   // also keeps the launch on the plain, non-cluster form
   const int mp = smallm_padded_rows(m);
@@ -527,24 +630,10 @@ int launch_gemm_smallm(const uint8_t* a_codes, int64_t lda, const float* a_scale
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   p.counters = reinterpret_cast<uint32_t*>(workspace);
   p.partials = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + kCounterBytes);
+  p.inter = inter;
   p.cluster = max_ctas > 0 ? 0 : smallm_cluster_size(p.tiles, p.groups, sms);
-  if (p.cluster >= 2) {
-    int crc;
-    switch (mp) {
-      case 16: crc = launch_clustered<16>(tmap_w, tmap_a, p, st); break;
-      case 32: crc = launch_clustered<32>(tmap_w, tmap_a, p, st); break;
-      case 64: crc = launch_clustered<64>(tmap_w, tmap_a, p, st); break;
-      default: crc = launch_clustered<128>(tmap_w, tmap_a, p, st); break;
-    }
-    if (crc != BFP8_ERR_UNSUPPORTED) return crc;
-    p.cluster = 0;
-  }
-  switch (mp) {
-    case 16: return launch<16>(tmap_w, tmap_a, p, grid, st);
-    case 32: return launch<32>(tmap_w, tmap_a, p, grid, st);
-    case 64: return launch<64>(tmap_w, tmap_a, p, grid, st);
-    default: return launch<128>(tmap_w, tmap_a, p, grid, st);
-  }
+  if (inter > 0) return dispatch<true>(mp, tmap_w, tmap_a, p, grid, st);
+  return dispatch<false>(mp, tmap_w, tmap_a, p, grid, st);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -612,5 +701,5 @@ extern "C" int bfp8_gemm_block128_noalloc(const uint8_t* a_codes, int64_t lda, c
   const size_t counter_bytes = static_cast<size_t>((n + BN - 1) / BN) * sizeof(uint32_t);
   BFP8_CUDA_TRY(cudaMemsetAsync(scratch, 0, counter_bytes, st));
   return launch_gemm_smallm(a_codes, lda, a_scales, ldsa, w_codes, ldw, w_scales, bias, out, out_dtype, ldo, m, n, k,
-                            scratch, status_dev, /*wait_limit=*/2000000000LL, kNoAllocMaxCtas, st);
+                            scratch, status_dev, /*wait_limit=*/2000000000LL, kNoAllocMaxCtas, /*inter=*/0, st);
 }

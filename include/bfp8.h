@@ -201,11 +201,16 @@ int bfp8_swiglu_interleave_weight(const uint8_t* w_codes, int64_t ld_src, uint8_
  * with 0 for g <= -88, and the product is rounded once.  w_codes is the output of
  * bfp8_swiglu_interleave_weight; w_scales ([2 * inter / 128, ceil(k/128)]) and bias ([2 * inter] or NULL)
  * keep the fused weight's original order (gate first).  Other requirements as bfp8_gemm_block128;
- * inter % 128 == 0.  Runs the large-tile schedule for every m; no workspace. */
+ * inter % 128 == 0.  One weight copy serves both buckets: with m <= 128 and a workspace of
+ * bfp8_gemm_block128_workspace_bytes(m, 2 * inter, k) bytes (256-byte aligned, first 64 KB zero as for
+ * bfp8_gemm_block128) the weight-streaming schedule runs with the same epilogue - bit-identical to the
+ * small-M GEMM over the un-interleaved weight followed by bfp8_silu_and_mul_bf16; without a workspace
+ * (NULL) or with larger m the large-tile schedule runs. */
 int bfp8_gemm_block128_swiglu(const uint8_t* a_codes, int64_t lda, const float* a_scales, int64_t ldsa,
                               const uint8_t* w_codes, int64_t ldw, const float* w_scales,
                               const float* bias, void* out, int64_t ldo,
-                              int64_t m, int64_t inter, int64_t k, uint32_t* status_dev, void* stream);
+                              int64_t m, int64_t inter, int64_t k,
+                              void* workspace, size_t workspace_bytes, uint32_t* status_dev, void* stream);
 
 /* The SwiGLU step on its own: out[r, c] = bf16( silu(gate_up[r, c]) * gate_up[r, inter + c] ), bf16 in and out.
  * Replaces gk_silu_and_mul_bf16_v1 (csrc/tpc/generic_dense/silu_and_mul_bf16.c:16-75, input [rows, 2 * inter], glue

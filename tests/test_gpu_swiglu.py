@@ -148,7 +148,7 @@ def test_standalone_silu_and_mul_matches_restatement(gk, rows, inter):
         w_plain, s_plain = gk.prepare_weight(codes.cuda(), s.cuda(), native_half=True)
         two_step = gk.silu_and_mul(gk.gemm_block_fp8(a_codes, a_scales, w_plain, s_plain, bias=b.cuda(), schedule=1))
         w_il, s_il = gk.prepare_weight_swiglu(codes.cuda(), s.cuda(), native_half=True)
-        fused = gk.gemm_block_fp8_swiglu(a_codes, a_scales, w_il, s_il, bias=b.cuda())
+        fused = gk.gemm_block_fp8_swiglu(a_codes, a_scales, w_il, s_il, bias=b.cuda(), small_m=False)   # same schedule as the GEMM above
         assert torch.equal(two_step, fused)
 
 
@@ -170,3 +170,47 @@ def test_fused_silu_quantizer_equals_the_two_kernels(gk, rows, inter, half):
     ref_values, ref_scales = block_fp8_ref.quantize_rows(h.cpu(), groups, half)      # values of the codes, [M, G, 128]
     assert torch.equal(codes.cpu().float(), ref_values.reshape(rows, -1)[:, :inter])
     assert torch.equal(scales.cpu(), ref_scales.reshape(rows, groups))
+
+
+@pytest.mark.parametrize("m,k,inter,bias", [(1, 4096, 14336, False), (8, 4096, 14336, True), (64, 4096, 14336, False),
+                                            (32, 2048, 1024, True), (16, 14336, 512, True), (100, 512, 4096, True),
+                                            (128, 1024, 2048, False), (5, 384, 128, True)])
+def test_decode_bucket_fused_swiglu_equals_gemm_then_silu_and_mul(gk, m, k, inter, bias):
+    # the weight-streaming schedule on the interleaved weight (one weight copy for prefill and decode) against the
+    # same schedule on the weight in its original order followed by the stand-alone kernel: bit for bit, in the
+    # stream-K form (more tiles than SMs), the one-CTA-per-tile form and the cluster form (few tiles)
+    x, codes, s, b = _problem(m, k, inter, seed=m * 11 + inter + k, bias=bias)
+    a_codes, a_scales = gk.quantize_act_1x128(x.cuda(), native_half=True)
+    bd = None if b is None else b.cuda()
+    w_plain, s_plain = gk.prepare_weight(codes.cuda(), s.cuda(), native_half=True)
+    w_il, s_il = gk.prepare_weight_swiglu(codes.cuda(), s.cuda(), native_half=True)
+    gate = gk.gemm_block_fp8(a_codes, a_scales, w_plain[:inter], s_plain[:inter // 128], bias=None if bd is None else bd[:inter],
+                             schedule=2)
+    up = gk.gemm_block_fp8(a_codes, a_scales, w_plain[inter:], s_plain[inter // 128:], bias=None if bd is None else bd[inter:],
+                           schedule=2)
+    want = gk.silu_and_mul(torch.cat([gate, up], dim=1).contiguous())
+    canvas = torch.full((m + 2, inter + 8), 7.0, dtype=torch.bfloat16, device="cuda")
+    got = gk.gemm_block_fp8_swiglu(a_codes, a_scales, w_il, s_il, bias=bd, out=canvas[:m, :inter])
+    assert bool((canvas[m:] == 7.0).all()) and bool((canvas[:, inter:] == 7.0).all())
+    again = gk.gemm_block_fp8_swiglu(a_codes, a_scales, w_il, s_il, bias=bd)
+    assert torch.equal(got, again)                                             # counters returned to zero, fixed order
+    # the tile decomposition along K is the same when gate and up have as many 128-row tiles together as the
+    # interleaved weight has (they always do), so the sums agree exactly where the split points agree; where the
+    # stream-K split differs between the two launches the fp32 association differs in the last bits: a factor may
+    # then round to the neighbouring bf16 value, which moves the product by up to one step more than its own rounding
+    # (and a factor that sits near zero moves by its absolute, not its relative, error: 1e-3 of the RMS covers that)
+    slack = 1e-3 * float(want.double().pow(2).mean().sqrt())
+    diff = (got.double() - want.double()).abs()
+    assert bool((diff <= 3.0 * _bf16_step(want) + slack).all()), float((diff - 3.0 * _bf16_step(want)).max())
+    assert float((got != want).float().mean()) < 5e-3
+    # and against the large-tile fused kernel on the same interleaved weight
+    large = gk.gemm_block_fp8_swiglu(a_codes, a_scales, w_il, s_il, bias=bd, small_m=False)
+    diff = (got.double() - large.double()).abs()
+    assert bool((diff <= 3.0 * _bf16_step(large) + slack).all()), float((diff - 3.0 * _bf16_step(large)).max())
+    assert float((got != large).float().mean()) < 5e-3
+    # end to end against the oracle's GEMM followed by the restated step
+    y64, ybf = block_fp8_ref.reference_rows(x, codes, s, native_half=True, bias=b)
+    want2 = swiglu_ref.silu_and_mul_bf16(ybf)
+    rms = float(want2.double().pow(2).mean().sqrt())
+    diff2 = (got.double().cpu() - want2.double()).abs()
+    assert bool((diff2 <= 3e-2 * rms + 3.0 * _bf16_step(want2)).all()), float(diff2.max())
