@@ -52,8 +52,8 @@ constexpr int kAccBufs = 4;
 constexpr int kWBytes = BN * BK;   // 16 KB of W per unit
 constexpr int kMaxStages = 10;
 constexpr int kSmemBudget = 200 * 1024;
-constexpr int kSwigluRows = 16;    // activation rows per exchange round of the SwiGLU form
-constexpr int kSwigluExBytes = kSwigluRows * 64 * 4;
+constexpr int kSwigluRows = 64;    // activation rows per exchange round of the SwiGLU form (fewer when MP is smaller)
+constexpr int kSwigluExBytes = 2 * kSwigluRows * 64 * 2;   // gate and up values as bf16
 
 template <int MP>
 struct Cfg {
@@ -94,30 +94,33 @@ struct Params {
   int inter;               // SwiGLU form: width of the gate and of the up projection (n = 2 * inter), else 0
 };
 
-// SwiGLU form: the up half of a tile (weight rows 64..127) hands bf16(up) to the gate half through `ex`
-// ([kRows][64] floats in shared memory); all 128 epilogue threads call this together (two named barriers inside).
-// `v[j]` is the thread's fp32 sum for activation row j0 + j (bias not yet added), `rows` how many are valid.
+// SwiGLU form: the two halves of a tile (weight rows 0..63: gate, 64..127: up, of the same 64 outputs) publish
+// their values - bias added, rounded to bf16 as the unfused GEMM would store them - in shared memory (`ex`:
+// [2][kRows][64] bf16), and then every thread finishes the outputs of its column for every second activation
+// row (gate threads the even rows, up threads the odd ones), so all four warps share the silu arithmetic.  All
+// 128 epilogue threads call this together (two named barriers inside).  `v[j]` is the thread's fp32 sum for
+// activation row j0 + j (bias not yet added), `rows` how many of them are valid.
 template <int kRows>
-__device__ __forceinline__ void swiglu_finish(const Params& p, float* ex, int tile, int wrow, const float* v,
+__device__ __forceinline__ void swiglu_finish(const Params& p, uint16_t* ex, int tile, int wrow, const float* v,
                                               int j0, int rows, bool write) {
   const bool gate = wrow < 64;
   const int o = gate ? wrow : wrow - 64;                       // output column inside the tile's 64
   const int col = tile * 64 + o;
   float b = 0.0f;
   if (p.bias != nullptr) b = __ldg(p.bias + (gate ? col : p.inter + col));
-  if (!gate) {
+  uint16_t* mine = ex + (gate ? 0 : kRows * 64);
 #pragma unroll
-    for (int j = 0; j < kRows; ++j)
-      if (j < rows) ex[j * 64 + o] = bf16_bits_to_float(float_to_bf16_bits(v[j] + b));
-  }
+  for (int j = 0; j < kRows; ++j)
+    if (j < rows) mine[j * 64 + o] = static_cast<uint16_t>(float_to_bf16_bits(v[j] + b));
   asm volatile("bar.sync 1, 128;" ::: "memory");
-  if (gate && write) {
+  if (write) {
     uint16_t* out = reinterpret_cast<uint16_t*>(p.out) + col;
 #pragma unroll
-    for (int j = 0; j < kRows; ++j) {
+    for (int jj = 0; jj < kRows / 2; ++jj) {
+      const int j = 2 * jj + (gate ? 0 : 1);
       if (j < rows && j0 + j < p.m) {
-        const float g = bf16_bits_to_float(float_to_bf16_bits(v[j] + b));
-        out[static_cast<int64_t>(j0 + j) * p.ldo] = static_cast<uint16_t>(float_to_bf16_bits(silu_mul(g, ex[j * 64 + o])));
+        const float g = bf16_bits_to_float(ex[j * 64 + o]), u = bf16_bits_to_float(ex[kRows * 64 + j * 64 + o]);
+        out[static_cast<int64_t>(j0 + j) * p.ldo] = static_cast<uint16_t>(float_to_bf16_bits(silu_mul(g, u)));
       }
     }
   }
@@ -142,7 +145,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
   SmemTail* tail = reinterpret_cast<SmemTail*>(smem + C::kStages * C::kStageBytes);
-  float* swiglu_ex = reinterpret_cast<float*>(tail + 1);       // [kSwigluRows][64], SwiGLU form only
+  uint16_t* swiglu_ex = reinterpret_cast<uint16_t*>(tail + 1);   // [2][rows per round][64] bf16, SwiGLU form only
   volatile uint32_t* abort_flag = &tail->abort_flag;
 
   const int warp = threadIdx.x >> 5;
@@ -339,9 +342,10 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         if (kSwiGLU) {
           // SwiGLU form: do_store is the same for all 128 threads, so the barriers inside are safe
           if (do_store) {
+            constexpr int kRound = MP < kSwigluRows ? MP : kSwigluRows;
 #pragma unroll
-            for (int j0 = 0; j0 < MP; j0 += kSwigluRows)
-              swiglu_finish<kSwigluRows>(p, swiglu_ex, tile, wrow, acc + j0, j0, kSwigluRows, alive);
+            for (int j0 = 0; j0 < MP; j0 += kRound)
+              swiglu_finish<kRound>(p, swiglu_ex, tile, wrow, acc + j0, j0, kRound, alive);
           }
         } else if (do_store && alive && col < p.n) {
           const float b = p.bias != nullptr ? __ldg(p.bias + col) : 0.0f;
@@ -427,17 +431,18 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
       if (kSwiGLU) {
         // SwiGLU form: this CTA's rows in rounds of kSwigluRows; every epilogue thread takes part in the barriers
         const float* mine = reinterpret_cast<const float*>(smem);
-        for (int jj0 = 0; jj0 < rows_per; jj0 += kSwigluRows) {
-          float v[kSwigluRows];
+        constexpr int kRound = 16;
+        for (int jj0 = 0; jj0 < rows_per; jj0 += kRound) {
+          float v[kRound];
 #pragma unroll
-          for (int q = 0; q < kSwigluRows; ++q) {
+          for (int q = 0; q < kRound; ++q) {
             float sum = 0.0f;
             if (jj0 + q < rows_per)
               for (int r = 0; r < cs; ++r) sum += mine[(r * rows_per + jj0 + q) * BN + wrow];   // rank order = K order
             v[q] = sum;
           }
-          swiglu_finish<kSwigluRows>(p, swiglu_ex, static_cast<int>(ctile), wrow, v, crank * rows_per + jj0,
-                                     min(kSwigluRows, rows_per - jj0), ok);
+          swiglu_finish<kRound>(p, swiglu_ex, static_cast<int>(ctile), wrow, v, crank * rows_per + jj0,
+                                min(kRound, rows_per - jj0), ok);
         }
       } else if (ok && col < p.n) {
         const float b = p.bias != nullptr ? __ldg(p.bias + col) : 0.0f;
@@ -576,9 +581,17 @@ size_t smallm_workspace_bytes(int64_t m, int64_t n, int max_ctas) {
 // end inside a tile (each such end costs a partial-sum round trip through the workspace).  With no more
 // tiles than SMs every tile gets the same whole number of CTAs, so a CTA holds exactly one K range of one
 // tile; with more tiles than SMs the unit list is cut evenly over all SMs.
-int smallm_grid(int64_t tiles, int64_t groups, int sms) {
+int smallm_grid(int64_t tiles, int64_t groups, int sms, int mp) {
   const long long units = tiles * groups;
   if (units < sms) return static_cast<int>(units);
+  if (tiles > sms && mp >= 32) {
+    // More tiles than SMs and many activation rows: the partial sums of a tile that ends in two CTAs (two fp32
+    // tiles of mp x 128 through global memory, a counter, a read-back) cost more than leaving some SMs idle, so
+    // the grid is the smallest one that gives every CTA the same number of whole tiles where the tile count
+    // allows it (224 tiles on 148 SMs: 112 CTAs with two tiles each).
+    const int64_t waves = (tiles + sms - 1) / sms;
+    return static_cast<int>((tiles + waves - 1) / waves);
+  }
   if (tiles <= sms) {
     long long per_tile = sms / tiles;
     if (per_tile > groups) per_tile = groups;
@@ -626,7 +639,7 @@ int launch_gemm_smallm(const uint8_t* a_codes, int64_t lda, const float* a_scale
   p.wait_limit = wait_limit;
   p.status = status_dev;
   const int sms = sm_count();
-  int grid = smallm_grid(p.tiles, p.groups, sms);
+  int grid = smallm_grid(p.tiles, p.groups, sms, mp);
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   p.counters = reinterpret_cast<uint32_t*>(workspace);
   p.partials = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + kCounterBytes);
