@@ -42,7 +42,7 @@ SIGNATURES = {
     "bfp8_rank_sum": (_int, [_ptr, _ptr, _i64, _int, _int, _ptr]),
     "bfp8_rank_sum_slices": (_int, [_ptr, _ptr, _i64, _int, _int, _ptr, _i64, _ptr]),
     "bfp8_gemm_block128_push": (_int, [_ptr, _i64, _ptr, _i64, _ptr, _i64, _ptr, _ptr, _int, _int,
-                                       _i64, _i64, _i64, _ptr, _ptr]),
+                                       _i64, _i64, _i64, _ptr, _sz, _ptr, _ptr]),
     "bfp8_peer_alloc": (_int, [_sz, _ptr]),
     "bfp8_peer_free": (_int, [_ptr]),
     "bfp8_peer_export": (_int, [_ptr, _ptr]),

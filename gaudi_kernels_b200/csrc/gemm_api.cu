@@ -6,6 +6,10 @@ struct PushTarget {
   const void* recv[8];
   int world, rank, rows;
 };
+struct SmallPush {
+  const void* recv[8];
+  int world, rank, rows;
+};
 int launch_gemm_large(const uint8_t* a_codes, int64_t lda, const float* a_scales, int64_t ldsa,
                       const uint8_t* w_codes, int64_t ldw, const float* w_scales, const float* bias, void* out,
                       int out_dtype, int64_t ldo, int64_t m, int64_t n, int64_t k, uint32_t* status_dev,
@@ -18,7 +22,8 @@ int launch_gemm_pair(const uint8_t* a_codes, int64_t lda, const float* a_scales,
 int launch_gemm_smallm(const uint8_t* a_codes, int64_t lda, const float* a_scales, int64_t ldsa,
                        const uint8_t* w_codes, int64_t ldw, const float* w_scales, const float* bias, void* out,
                        int out_dtype, int64_t ldo, int64_t m, int64_t n, int64_t k, void* workspace,
-                       uint32_t* status_dev, long long wait_limit, int max_ctas, int inter, cudaStream_t st);
+                       uint32_t* status_dev, long long wait_limit, int max_ctas, int inter, const SmallPush* push,
+                       cudaStream_t st);
 int launch_gemm_channel(const uint8_t* a_codes, int64_t lda, const float* a_scales, const uint8_t* w_codes,
                         int64_t ldw, const float* w_scales, const float* bias, void* out, int out_dtype, int64_t ldo,
                         int64_t m, int64_t n, int64_t k, uint32_t* status_dev, long long wait_limit, int max_ctas,
@@ -69,7 +74,7 @@ extern "C" int bfp8_gemm_block128_ex(const uint8_t* a_codes, int64_t lda, const 
     if (!aligned(workspace, 256)) return BFP8_ERR_ALIGN;
     if (sm_count() > kMaxCtas) return BFP8_ERR_UNSUPPORTED;
     return launch_gemm_smallm(a_codes, lda, a_scales, ldsa, w_codes, ldw, w_scales, bias, out, out_dtype, ldo,
-                              m, n, k, workspace, status_dev, limit, max_ctas, /*inter=*/0, st);
+                              m, n, k, workspace, status_dev, limit, max_ctas, /*inter=*/0, /*push=*/nullptr, st);
   }
   if (schedule == 3)
     return launch_gemm_pair(a_codes, lda, a_scales, ldsa, w_codes, ldw, w_scales, bias, out, out_dtype, ldo, m, n, k,
@@ -163,7 +168,7 @@ extern "C" int bfp8_gemm_block128_swiglu(const uint8_t* a_codes, int64_t lda, co
     if (sm_count() > kMaxCtas) return BFP8_ERR_UNSUPPORTED;
     return launch_gemm_smallm(a_codes, lda, a_scales, ldsa, w_codes, ldw, w_scales, bias, out, BFP8_OUT_BF16, ldo, m,
                               2 * inter, k, workspace, status_dev, kDefaultWaitLimit, 0, static_cast<int>(inter),
-                              static_cast<cudaStream_t>(stream));
+                              /*push=*/nullptr, static_cast<cudaStream_t>(stream));
   }
   return launch_gemm_large(a_codes, lda, a_scales, ldsa, w_codes, ldw, w_scales, bias, out, BFP8_OUT_BF16, ldo,
                            m, 2 * inter, k, status_dev, kDefaultWaitLimit, 0, /*band=*/0, static_cast<int>(inter),
@@ -225,12 +230,15 @@ extern "C" int bfp8_silu_and_mul_bf16(const uint16_t* gate_up, int64_t ld_in, ui
 extern "C" int bfp8_gemm_block128_push(const uint8_t* a_codes, int64_t lda, const float* a_scales, int64_t ldsa,
                                        const uint8_t* w_codes, int64_t ldw, const float* w_scales,
                                        void* const* recv, int rank, int world_size,
-                                       int64_t m, int64_t n, int64_t k, uint32_t* status_dev, void* stream) {
+                                       int64_t m, int64_t n, int64_t k,
+                                       void* workspace, size_t workspace_bytes, uint32_t* status_dev, void* stream) {
   if (!a_codes || !a_scales || !w_codes || !w_scales || !recv || !status_dev) return BFP8_ERR_NULL;
   if (m <= 0 || n <= 0 || k <= 0 || m > (1 << 30) || n > (1 << 30) || k > (1 << 30)) return BFP8_ERR_SHAPE;
   if (world_size < 2 || world_size > 8 || rank < 0 || rank >= world_size) return BFP8_ERR_UNSUPPORTED;
   if (lda < k || ldw < k || ldsa < m) return BFP8_ERR_SHAPE;
-  if (m % (128 * world_size) != 0 || n % 64 != 0) return BFP8_ERR_UNSUPPORTED;
+  // decode bucket: the weight-streaming schedule stores each activation row to the GPU that owns it
+  const bool small = m <= kSmallMRows && m % world_size == 0 && n % 64 == 0 && smallm_supported(n) && workspace != nullptr;
+  if (!small && (m % (128 * world_size) != 0 || n % 64 != 0)) return BFP8_ERR_UNSUPPORTED;
   if (!aligned(a_codes, 16) || !aligned(w_codes, 16) || lda % 16 != 0 || ldw % 16 != 0) return BFP8_ERR_ALIGN;
   if (!aligned(a_scales, 4) || !aligned(w_scales, 4) || !aligned(status_dev, 4)) return BFP8_ERR_ALIGN;
   PushTarget t = {};
@@ -242,6 +250,19 @@ extern "C" int bfp8_gemm_block128_push(const uint8_t* a_codes, int64_t lda, cons
   t.world = world_size;
   t.rank = rank;
   t.rows = static_cast<int>(m / world_size);
+  if (small) {
+    if (workspace_bytes < bfp8_gemm_block128_workspace_bytes(m, n, k)) return BFP8_ERR_WORKSPACE;
+    if (!aligned(workspace, 256)) return BFP8_ERR_ALIGN;
+    if (sm_count() > kMaxCtas) return BFP8_ERR_UNSUPPORTED;
+    SmallPush sp = {};
+    for (int o = 0; o < world_size; ++o) sp.recv[o] = t.recv[o];
+    sp.world = t.world;
+    sp.rank = t.rank;
+    sp.rows = t.rows;
+    return launch_gemm_smallm(a_codes, lda, a_scales, ldsa, w_codes, ldw, w_scales, nullptr, const_cast<void*>(t.recv[rank]),
+                              BFP8_OUT_BF16, n, m, n, k, workspace, status_dev, kDefaultWaitLimit, 0, /*inter=*/0, &sp,
+                              static_cast<cudaStream_t>(stream));
+  }
   return launch_gemm_large(a_codes, lda, a_scales, ldsa, w_codes, ldw, w_scales, nullptr, const_cast<void*>(t.recv[rank]),
                            BFP8_OUT_BF16, n, m, n, k, status_dev, kDefaultWaitLimit, 0, /*band=*/0, /*inter=*/0, &t,
                            static_cast<cudaStream_t>(stream));

@@ -41,6 +41,12 @@
 
 namespace bfp8 {
 
+// Destination of the push form: recv[o] is GPU o's receive area ([world][rows][n] bf16, mapped in this process).
+struct SmallPush {
+  const void* recv[8];
+  int world, rank, rows;
+};
+
 namespace {
 
 constexpr int BN = 128;            // weight rows per tile = one scale block
@@ -92,7 +98,20 @@ struct Params {
   uint32_t* status;
   int cluster;             // CTAs per tile when the kernel runs as clusters (kCluster), else unused
   int inter;               // SwiGLU form: width of the gate and of the up projection (n = 2 * inter), else 0
+  // Push form (row-parallel GEMM, bf16): activation row j of this rank's partial goes to GPU j / push_rows, into
+  // slot push_rank of its receive area [push_world][push_rows][n]; push_world == 0 stores to `out` as usual
+  int push_world, push_rank, push_rows;
+  uint16_t* push_recv[8];
 };
+
+// Where activation row j of a bf16 result goes (column 0 of that row).
+__device__ __forceinline__ uint16_t* out_row_bf16(const Params& p, int j) {
+  if (p.push_world > 0) {
+    const int owner = j / p.push_rows;
+    return p.push_recv[owner] + (static_cast<int64_t>(p.push_rank) * p.push_rows + (j - owner * p.push_rows)) * p.n;
+  }
+  return reinterpret_cast<uint16_t*>(p.out) + static_cast<int64_t>(j) * p.ldo;
+}
 
 // SwiGLU form: the two halves of a tile (weight rows 0..63: gate, 64..127: up, of the same 64 outputs) publish
 // their values - bias added, rounded to bf16 as the unfused GEMM would store them - in shared memory (`ex`:
@@ -350,10 +369,9 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         } else if (do_store && alive && col < p.n) {
           const float b = p.bias != nullptr ? __ldg(p.bias + col) : 0.0f;
           if (p.out_bf16) {
-            uint16_t* o = reinterpret_cast<uint16_t*>(p.out) + col;
 #pragma unroll
             for (int j = 0; j < MP; ++j)
-              if (j < p.m) o[static_cast<int64_t>(j) * p.ldo] = static_cast<uint16_t>(float_to_bf16_bits(acc[j] + b));
+              if (j < p.m) out_row_bf16(p, j)[col] = static_cast<uint16_t>(float_to_bf16_bits(acc[j] + b));
           } else {
             float* o = reinterpret_cast<float*>(p.out) + col;
 #pragma unroll
@@ -454,7 +472,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
           for (int r = 0; r < cs; ++r) sum += mine[(r * rows_per + jj) * BN + wrow];   // rank order = K order
           sum += b;
           if (p.out_bf16)
-            reinterpret_cast<uint16_t*>(p.out)[static_cast<int64_t>(j) * p.ldo + col] = static_cast<uint16_t>(float_to_bf16_bits(sum));
+            out_row_bf16(p, j)[col] = static_cast<uint16_t>(float_to_bf16_bits(sum));
           else
             reinterpret_cast<float*>(p.out)[static_cast<int64_t>(j) * p.ldo + col] = sum;
         }
@@ -613,8 +631,10 @@ int smallm_cluster_size(int64_t tiles, int64_t groups, int sms) {
 int launch_gemm_smallm(const uint8_t* a_codes, int64_t lda, const float* a_scales, int64_t ldsa,
                        const uint8_t* w_codes, int64_t ldw, const float* w_scales, const float* bias, void* out,
                        int out_dtype, int64_t ldo, int64_t m, int64_t n, int64_t k, void* workspace,
-                       uint32_t* status_dev, long long wait_limit, int max_ctas, int inter, cudaStream_t st) {
+                       uint32_t* status_dev, long long wait_limit, int max_ctas, int inter, const SmallPush* push,
+                       cudaStream_t st) {
   // inter > 0 selects the SwiGLU form: W has n = 2 * inter interleaved rows, `out` is bf16 [m, inter]
+  // push != nullptr selects the push form: bf16 rows go to the receive areas of the GPUs that own them
   // max_ctas > 0 (a caller-imposed CTA limit, used by tests and by the entry point with the built-in scratch)
   // also keeps the launch on the plain, non-cluster form
   const int mp = smallm_padded_rows(m);
@@ -644,6 +664,18 @@ int launch_gemm_smallm(const uint8_t* a_codes, int64_t lda, const float* a_scale
   p.counters = reinterpret_cast<uint32_t*>(workspace);
   p.partials = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + kCounterBytes);
   p.inter = inter;
+  p.push_world = p.push_rank = 0;
+  p.push_rows = 1;
+  for (int o = 0; o < 8; ++o) p.push_recv[o] = nullptr;
+  if (push != nullptr) {
+    if (out_dtype != BFP8_OUT_BF16 || inter > 0 || push->world < 2 || push->world > 8 || push->rows <= 0 ||
+        m != static_cast<int64_t>(push->rows) * push->world)
+      return BFP8_ERR_UNSUPPORTED;
+    p.push_world = push->world;
+    p.push_rank = push->rank;
+    p.push_rows = push->rows;
+    for (int o = 0; o < push->world; ++o) p.push_recv[o] = reinterpret_cast<uint16_t*>(const_cast<void*>(push->recv[o]));
+  }
   p.cluster = max_ctas > 0 ? 0 : smallm_cluster_size(p.tiles, p.groups, sms);
   if (inter > 0) return dispatch<true>(mp, tmap_w, tmap_a, p, grid, st);
   return dispatch<false>(mp, tmap_w, tmap_a, p, grid, st);
@@ -714,5 +746,5 @@ extern "C" int bfp8_gemm_block128_noalloc(const uint8_t* a_codes, int64_t lda, c
   const size_t counter_bytes = static_cast<size_t>((n + BN - 1) / BN) * sizeof(uint32_t);
   BFP8_CUDA_TRY(cudaMemsetAsync(scratch, 0, counter_bytes, st));
   return launch_gemm_smallm(a_codes, lda, a_scales, ldsa, w_codes, ldw, w_scales, bias, out, out_dtype, ldo, m, n, k,
-                            scratch, status_dev, /*wait_limit=*/2000000000LL, kNoAllocMaxCtas, /*inter=*/0, st);
+                            scratch, status_dev, /*wait_limit=*/2000000000LL, kNoAllocMaxCtas, /*inter=*/0, /*push=*/nullptr, st);
 }

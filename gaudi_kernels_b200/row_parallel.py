@@ -178,8 +178,11 @@ def reduce_scatter_rows(exchange, partial, bias=None, out=None, out_dtype=None):
 
 
 def push_supported(m, n, world, partial_dtype=torch.bfloat16):
-    """True where the GEMM can scatter its tiles itself (bfp8_gemm_block128_push)."""
-    return world >= 2 and partial_dtype == torch.bfloat16 and m % (BLOCK * world) == 0 and n % 64 == 0
+    """True where the GEMM can scatter its result itself (bfp8_gemm_block128_push): M a multiple of 128 * world
+    (large-tile schedule) or the decode bucket M <= 128 with M a multiple of world (weight-streaming schedule)."""
+    if world < 2 or partial_dtype != torch.bfloat16 or n % 64 != 0:
+        return False
+    return m % (BLOCK * world) == 0 or (m <= 128 and m % world == 0)
 
 
 def gemm_k_sharded(a_codes_local, a_scales_local, w_codes_local, w_scales_local, exchange, bias=None,
@@ -192,14 +195,15 @@ def gemm_k_sharded(a_codes_local, a_scales_local, w_codes_local, w_scales_local,
 
     fused    the GEMM's epilogue stores every bf16 tile into the receive area of the GPU that owns its rows
              (bfp8_gemm_block128_push), so the exchange overlaps the math; after the barrier each rank holds the
-             `gathered` layout of rank_sum.c and sums it locally.  Needs M % (128 * world) == 0, N % 64 == 0.
+             `gathered` layout of rank_sum.c and sums it locally.  Needs N % 64 == 0 and M % (128 * world) == 0, or
+             the decode bucket M <= 128 with M % world == 0 (each activation row is stored to its owner).
     unfused  the partial is written locally in `partial_dtype` (bf16 or fp32) and reduce_scatter_rows reads the
              peers' rows over NVLink.  fp32 partials take any shape; bf16 partials need N % 8 == 0 (their rows are
              stored in 16-byte units, BFP8_ERR_ALIGN otherwise).
     Either form reports an expired bounded wait (GEMM or barrier) through exchange.timed_out().
     fused=None picks the fused form where it applies.
     """
-    from .block_fp8_gemm import _group_major, gemm_block_fp8
+    from .block_fp8_gemm import _group_major, _workspace, gemm_block_fp8
     m, k = a_codes_local.shape
     n = w_codes_local.shape[0]
     world, rank = exchange.world, exchange.rank
@@ -207,7 +211,8 @@ def gemm_k_sharded(a_codes_local, a_scales_local, w_codes_local, w_scales_local,
     if fused is None:
         fused = can_push
     if fused and not can_push:
-        raise ValueError("the fused form needs bf16 partials, M % (128 * world) == 0, N % 64 == 0 and K % 16 == 0")
+        raise ValueError("the fused form needs bf16 partials, N % 64 == 0, K % 16 == 0 and M % (128 * world) == 0 "
+                         "(or M <= 128 with M % world == 0)")
     if not fused:
         partial = exchange.partial(m, n, partial_dtype)
         gemm_block_fp8(a_codes_local, a_scales_local, w_codes_local, w_scales_local, out=partial,
@@ -231,10 +236,12 @@ def gemm_k_sharded(a_codes_local, a_scales_local, w_codes_local, w_scales_local,
     with torch.cuda.device(dev):
         sa, ldsa = _group_major(a_scales_local, m, g)
         recv = (ctypes.c_void_p * world)(*exchange.ptrs)
+        ws_bytes = lib.bfp8_gemm_block128_workspace_bytes(m, n, k) if m <= 128 else 0
+        ws = _workspace(dev, ws_bytes) if ws_bytes else None
         rc = lib.bfp8_gemm_block128_push(
             a_codes_local.data_ptr(), a_codes_local.stride(0), sa.data_ptr(), ldsa, w_codes_local.data_ptr(),
             w_codes_local.stride(0), w_scales_local.data_ptr(), recv, rank, world, m, n, k,
-            exchange.status.data_ptr() + 8, _stream_ptr())
+            ws.data_ptr() if ws is not None else None, ws_bytes, exchange.status.data_ptr() + 8, _stream_ptr())
         _lib.check(rc, "bfp8_gemm_block128_push")
         exchange.barrier()                                   # every rank's tiles have landed here
         slices = (ctypes.c_void_p * world)(*[exchange.ptrs[rank] + r * rows * n * 2 for r in range(world)])

@@ -251,13 +251,17 @@ int bfp8_rank_sum_slices(const void* const* slices, void* dst, int64_t elems, in
  * device pointers; recv[o] is rank o's receive area, bf16 [world_size][m / world_size][n] contiguous (peer
  * memory from bfp8_peer_open for o != rank), and this rank's rows [o R, (o + 1) R), R = m / world_size, land in
  * recv[o][rank].  After a bfp8_peer_barrier, recv[rank] is exactly the `gathered` operand of bfp8_rank_sum
- * (csrc/tpc/generic_dense/rank_sum.c:2: world_size contiguous slices).  Requires m % (128 * world_size) == 0 and
- * n % 64 == 0 (BFP8_ERR_UNSUPPORTED otherwise; use bfp8_gemm_block128 + bfp8_rank_sum_slices then); no bias
- * here - add it in the sum.  No TMA load of this kernel touches peer memory and nothing is multicast. */
+ * (csrc/tpc/generic_dense/rank_sum.c:2: world_size contiguous slices).  Two shapes are taken, both with
+ * n % 64 == 0: m % (128 * world_size) == 0 (large-tile schedule, bulk tensor stores; no workspace needed), and the
+ * decode bucket m <= 128 with m % world_size == 0 (weight-streaming schedule, plain peer stores of each activation
+ * row to its owner; needs a workspace of bfp8_gemm_block128_workspace_bytes(m, n, k) bytes, as bfp8_gemm_block128).
+ * Anything else returns BFP8_ERR_UNSUPPORTED (use bfp8_gemm_block128 + bfp8_rank_sum_slices then).  No bias here -
+ * add it in the sum.  No TMA load of this kernel touches peer memory and nothing is multicast. */
 int bfp8_gemm_block128_push(const uint8_t* a_codes, int64_t lda, const float* a_scales, int64_t ldsa,
                             const uint8_t* w_codes, int64_t ldw, const float* w_scales,
                             void* const* recv, int rank, int world_size,
-                            int64_t m, int64_t n, int64_t k, uint32_t* status_dev, void* stream);
+                            int64_t m, int64_t n, int64_t k,
+                            void* workspace, size_t workspace_bytes, uint32_t* status_dev, void* stream);
 
 /* Device memory that other processes on the same machine can map (one process per GPU).  These have no
  * counterpart in the reference, whose cross-device exchange lives in the external runtime

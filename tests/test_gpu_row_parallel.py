@@ -90,7 +90,9 @@ def _worker(rank, world, port, m, k, n, partial_name, use_bias, result_queue):
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 @pytest.mark.parametrize("m,k,n,partial,bias", [(256, 1024, 512, "bfloat16", True), (300, 1152, 640, "float32", False),
-                                                 (5, 2048, 1024, "bfloat16", False), (2048, 4096, 2048, "bfloat16", True)])
+                                                 (5, 2048, 1024, "bfloat16", False), (2048, 4096, 2048, "bfloat16", True),
+                                                 (8, 2048, 1024, "bfloat16", True), (64, 14336, 4096, "bfloat16", False),
+                                                 (128, 512, 8192, "bfloat16", False)])
 def test_row_parallel_gemm_two_gpus(m, k, n, partial, bias):
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
@@ -111,4 +113,5 @@ def test_row_parallel_gemm_two_gpus(m, k, n, partial, bias):
     assert sorted(r[0] for r in results) == [0, 1]
     for rank, state, info in results:
         assert state == "ok", "rank %d: %s" % (rank, info)
-        assert info[1] == (partial == "bfloat16" and m % 256 == 0 and n % 64 == 0)     # which form ran
+        # which form ran: the fused one for M a multiple of 128 * 2, and for the decode bucket with even M
+        assert info[1] == (partial == "bfloat16" and n % 64 == 0 and (m % 256 == 0 or (m <= 128 and m % 2 == 0)))
