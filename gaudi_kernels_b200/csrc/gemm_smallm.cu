@@ -368,10 +368,15 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
           }
         } else if (do_store && alive && col < p.n) {
           const float b = p.bias != nullptr ? __ldg(p.bias + col) : 0.0f;
-          if (p.out_bf16) {
+          if (p.out_bf16 && p.push_world > 0) {
 #pragma unroll
             for (int j = 0; j < MP; ++j)
               if (j < p.m) out_row_bf16(p, j)[col] = static_cast<uint16_t>(float_to_bf16_bits(acc[j] + b));
+          } else if (p.out_bf16) {
+            uint16_t* o = reinterpret_cast<uint16_t*>(p.out) + col;
+#pragma unroll
+            for (int j = 0; j < MP; ++j)
+              if (j < p.m) o[static_cast<int64_t>(j) * p.ldo] = static_cast<uint16_t>(float_to_bf16_bits(acc[j] + b));
           } else {
             float* o = reinterpret_cast<float*>(p.out) + col;
 #pragma unroll
@@ -497,7 +502,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
 template <int MP, bool kSwiGLU>
 int launch(const CUtensorMap& tmap_w, const CUtensorMap& tmap_a, const Params& p, int grid, cudaStream_t st) {
   using C = Cfg<MP>;
-  constexpr int smem = 1024 + C::kStages * C::kStageBytes + sizeof(SmemTail) + kSwigluExBytes;
+  constexpr int smem = 1024 + C::kStages * C::kStageBytes + sizeof(SmemTail) + (kSwiGLU ? kSwigluExBytes : 0);
   static bool done[64] = {};
   const int rc = ensure_smem_limit(gemm_smallm_kernel<MP, false, kSwiGLU>, smem, done);
   if (rc != BFP8_OK) return rc;
@@ -521,7 +526,7 @@ int launch(const CUtensorMap& tmap_w, const CUtensorMap& tmap_a, const Params& p
 template <int MP, bool kSwiGLU>
 int launch_clustered(const CUtensorMap& tmap_w, const CUtensorMap& tmap_a, const Params& p, cudaStream_t st) {
   using C = Cfg<MP>;
-  constexpr int smem = 1024 + C::kStages * C::kStageBytes + sizeof(SmemTail) + kSwigluExBytes;
+  constexpr int smem = 1024 + C::kStages * C::kStageBytes + sizeof(SmemTail) + (kSwiGLU ? kSwigluExBytes : 0);
   static_assert(MP * BN * 4 <= C::kStages * C::kStageBytes, "the exchange area reuses the pipeline buffers");
   static bool done[64] = {};
   const int rc = ensure_smem_limit(gemm_smallm_kernel<MP, true, kSwiGLU>, smem, done);
