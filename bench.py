@@ -44,6 +44,7 @@ WORKLOADS = {
     "ffn70b": (16384, 8192, 28672),
     "prefill_up_quarter": (2048, 4096, 14336),     # same kernel and K/N, a quarter of the rows: the size used for ncu captures
     "prefill_up_token_channel": (8192, 4096, 14336),   # same shape, per-token / per-channel scales (no per-block promotion)
+    "ffn70b_slice_quarter": (4096, 8192, 3584),    # a quarter of the rows of one rank's slice at 8 GPUs (M=16384, N=28672 / 8): ncu captures
     "decode_m64": (64, 4096, 14336),               # the decode bucket's largest M: the weight-streaming schedule, HBM-bound
     "ffn70b_down": (16384, 28672, 8192),           # row-parallel: W split on K, rank-order sum over peer memory (N > 1 only)
     "codec": (8192, 8192, 0),                      # the elementwise codec configuration, fp32 [8192, 8192] (no GEMM)
@@ -97,6 +98,18 @@ def profiled_traffic(workload):
         with open(path) as f:
             return json.load(f).get(workload)
     return None
+
+
+def sliced_traffic(workload, m, k, n_local):
+    """DRAM bytes per launch of one rank's slice of the multi-GPU shape, scaled from the ncu capture of a quarter of
+    its rows (profiles/gemm_block128_dram_traffic.md): A and the output grow with M, the W slice does not.  Only the
+    8-GPU slice (N / 8 columns) was captured; other slices give None."""
+    q = profiled_traffic("ffn70b_slice_quarter")
+    qm, qk, qn = WORKLOADS["ffn70b_slice_quarter"]
+    if workload != "ffn70b" or q is None or (k, n_local) != (qk, qn):
+        return None
+    w_bytes = qk * qn
+    return int((q - w_bytes) * (m / qm) + w_bytes)
 
 
 class ClockSampler:
@@ -874,7 +887,7 @@ def main():
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak_tflops, "unit": "TFLOP/s",
                      "frac": achieved / peak_tflops, "peak_source": peak_how + " - of measured",
                      "frac_of_nominal_4500": achieved / 4500.0,
-                     "traffic": profiled_traffic(workload),
+                     "traffic": profiled_traffic(workload) if world == 1 else sliced_traffic(workload, m, k, n_local),
                      "kernel": "gemm_channel_kernel<bf16 out>" if token_channel else "gemm_block128_kernel<bf16 out>",
                      "launch_ms_median": statistics.median(step_ms)},
         "clocks": clocks,

@@ -5,6 +5,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "bfp8.h"
 
 namespace bfp8 {
@@ -33,14 +35,19 @@ int make_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* bas
                        uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer,
                        CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B);
 
-// Raise a kernel's dynamic shared-memory limit once per device (the attribute is per device context).
+// One flag per device ordinal, shared by the host threads that call into the library.
+typedef std::atomic<bool> DeviceFlags[64];
+
+// Raise a kernel's dynamic shared-memory limit once per device (the attribute is per device context; setting it
+// twice from two threads is harmless, so a relaxed flag is enough).  The caches of this library are keyed by
+// device ordinal: they do not survive cudaDeviceReset.
 template <typename Kernel>
-inline int ensure_smem_limit(Kernel kernel, int bytes, bool (&done)[64]) {
+inline int ensure_smem_limit(Kernel kernel, int bytes, DeviceFlags& done) {
   int dev = 0;
   BFP8_CUDA_TRY(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64 || !done[dev]) {
+  if (dev < 0 || dev >= 64 || !done[dev].load(std::memory_order_acquire)) {
     BFP8_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
-    if (dev >= 0 && dev < 64) done[dev] = true;
+    if (dev >= 0 && dev < 64) done[dev].store(true, std::memory_order_release);
   }
   return BFP8_OK;
 }

@@ -310,7 +310,7 @@ int launch_gemm_channel(const uint8_t* a_codes, int64_t lda, const float* a_scal
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   if (tiles < grid) grid = tiles;
   auto kern = bf16 ? gemm_channel_kernel<true> : gemm_channel_kernel<false>;
-  static bool done[2][64] = {};
+  static DeviceFlags done[2];
   rc = ensure_smem_limit(kern, kSmemBytes, done[bf16 ? 1 : 0]);
   if (rc != BFP8_OK) return rc;
   kern<<<grid, kThreads, kSmemBytes, st>>>(tmap_a, tmap_w, tmap_out, p);

@@ -438,7 +438,7 @@ int launch_gemm_pair(const uint8_t* a_codes, int64_t lda, const float* a_scales,
   if (max_ctas > 1 && max_ctas / 2 < pairs) pairs = max_ctas / 2;
   if (tiles < pairs) pairs = tiles;
   auto kern = bf16 ? gemm_pair_kernel<true> : gemm_pair_kernel<false>;
-  static bool done[2][64] = {};
+  static DeviceFlags done[2];
   rc = ensure_smem_limit(kern, kSmemBytes, done[bf16 ? 1 : 0]);
   if (rc != BFP8_OK) return rc;
   cudaLaunchConfig_t cfg = {};

@@ -503,7 +503,7 @@ template <int MP, bool kSwiGLU>
 int launch(const CUtensorMap& tmap_w, const CUtensorMap& tmap_a, const Params& p, int grid, cudaStream_t st) {
   using C = Cfg<MP>;
   constexpr int smem = 1024 + C::kStages * C::kStageBytes + sizeof(SmemTail) + (kSwiGLU ? kSwigluExBytes : 0);
-  static bool done[64] = {};
+  static DeviceFlags done;
   const int rc = ensure_smem_limit(gemm_smallm_kernel<MP, false, kSwiGLU>, smem, done);
   if (rc != BFP8_OK) return rc;
   // launched so that the set-up of this kernel may overlap the tail of the previous kernel in the stream
@@ -528,7 +528,7 @@ int launch_clustered(const CUtensorMap& tmap_w, const CUtensorMap& tmap_a, const
   using C = Cfg<MP>;
   constexpr int smem = 1024 + C::kStages * C::kStageBytes + sizeof(SmemTail) + (kSwiGLU ? kSwigluExBytes : 0);
   static_assert(MP * BN * 4 <= C::kStages * C::kStageBytes, "the exchange area reuses the pipeline buffers");
-  static bool done[64] = {};
+  static DeviceFlags done;
   const int rc = ensure_smem_limit(gemm_smallm_kernel<MP, true, kSwiGLU>, smem, done);
   if (rc != BFP8_OK) return rc;
   cudaLaunchConfig_t cfg = {};
@@ -546,15 +546,15 @@ int launch_clustered(const CUtensorMap& tmap_w, const CUtensorMap& tmap_a, const
   cfg.attrs = attr;
   cfg.numAttrs = 2;
   // co-residency of all clusters, asked once per device and cluster size (index log2(cluster) - 1)
-  static int max_clusters[64][3] = {};
+  static std::atomic<int> max_clusters[64][3];
   int dev = 0;
   BFP8_CUDA_TRY(cudaGetDevice(&dev));
   const int slot = p.cluster == 2 ? 0 : p.cluster == 4 ? 1 : 2;
-  int cap = (dev >= 0 && dev < 64) ? max_clusters[dev][slot] : 0;
+  int cap = (dev >= 0 && dev < 64) ? max_clusters[dev][slot].load(std::memory_order_acquire) : 0;
   if (cap == 0) {
     BFP8_CUDA_TRY(cudaOccupancyMaxActiveClusters(&cap, gemm_smallm_kernel<MP, true, kSwiGLU>, &cfg));
     if (cap <= 0) cap = -1;
-    if (dev >= 0 && dev < 64) max_clusters[dev][slot] = cap;
+    if (dev >= 0 && dev < 64) max_clusters[dev][slot].store(cap, std::memory_order_release);
   }
   if (cap < p.tiles) return BFP8_ERR_UNSUPPORTED;
   BFP8_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_smallm_kernel<MP, true, kSwiGLU>, tmap_w, tmap_a, p));

@@ -517,7 +517,7 @@ int launch_gemm_large(const uint8_t* a_codes, int64_t lda, const float* a_scales
   if (inter > 0 && !bf16) return BFP8_ERR_UNSUPPORTED;
   auto kern = inter > 0 ? gemm_block128_kernel<true, true>
                         : (bf16 ? gemm_block128_kernel<true, false> : gemm_block128_kernel<false, false>);
-  static bool done[3][64] = {};
+  static DeviceFlags done[3];
   rc = ensure_smem_limit(kern, kSmemBytes, done[inter > 0 ? 2 : (bf16 ? 1 : 0)]);
   if (rc != BFP8_OK) return rc;
   kern<<<grid, kThreads, kSmemBytes, st>>>(tmap_a, tmap_w, tmap_out, pmaps, p);

@@ -13,7 +13,9 @@
  *   - The library's only mutable global state is caches of facts about the device (driver entry points, SM
  *     count, per-kernel shared-memory and cluster limits) and the fixed scratch of
  *     bfp8_gemm_block128_noalloc; calls are re-entrant and may be issued from several host threads on
- *     different streams (that one entry point excepted, see there).
+ *     different streams (that one entry point excepted, see there).  The caches are keyed by device ordinal
+ *     and are not rebuilt after cudaDeviceReset: a process that resets a device must not call the library
+ *     on it again.
  *
  * These conventions mirror the reference glue's: integer status codes instead of exceptions, caller-owned
  * buffers, and a size query before any call that needs scratch (two-phase protocol of
