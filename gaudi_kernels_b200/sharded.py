@@ -87,7 +87,7 @@ def reference_sharded(x_local, weight_local, scales_local, *, native_half=True, 
     """
     from . import _lib
     from .block_fp8_gemm import _copy_stream, _workspaces, _WAIT_TIMEOUT_MSG, gemm_block_fp8
-    from .fp8_codec import _device_for, _read_status, _status_buffer, _stream_ptr
+    from .fp8_codec import _device_for, _status_buffer, _stream_ptr
     if (x_local.dtype != torch.bfloat16 or weight_local.dtype != torch.float8_e4m3fn or scales_local.dtype != torch.float32
             or x_local.ndim != 2 or weight_local.ndim != 2 or x_local.shape[1] != weight_local.shape[1]):
         raise ValueError("BF16 activation rows, original OCP FP8 weight slice and FP32 scales required")
@@ -147,7 +147,12 @@ def reference_sharded(x_local, weight_local, scales_local, *, native_half=True, 
                 keep.append(yr)
             main.wait_stream(side)
             y = out
-        status = _read_status(st)[1]
+        # a condition seen by one rank (a non-finite activation in its rows, a bad code in its weight slice, an
+        # expired wait) invalidates every rank's slice: the status bits are OR-ed over the group (as a MAX over
+        # one flag per bit, NCCL has no bitwise reduction) before anybody reads them
+        bits = (st[2:3] >> torch.arange(4, dtype=torch.int32, device=dev)) & 1
+        dist.all_reduce(bits, op=dist.ReduceOp.MAX, group=group)
+        status = sum(int(b) << i for i, b in enumerate(bits.cpu().tolist()))   # synchronises: also completes the copies
         if status & (_lib.STATUS_NONFINITE_CODE | _lib.STATUS_BAD_SCALE | _lib.STATUS_NONFINITE_INPUT):
             raise ValueError("finite original inputs required")
         if status & _lib.STATUS_WAIT_TIMEOUT:
