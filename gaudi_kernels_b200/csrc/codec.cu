@@ -230,7 +230,7 @@ __device__ __forceinline__ float silu_mul_bf16_rounded(float g, float u) {
 // bf16(silu(gate) * up) - gk_silu_and_mul_bf16_v1 followed by the 1x128 quantizer, without the round trip of the
 // intermediate tensor through HBM.
 template <bool kVec, bool kSilu>
-__global__ void __launch_bounds__(kActThreads, 4)
+__global__ void __launch_bounds__(kActThreads, kSilu ? 4 : 6)
 quant_act_1x128_kernel(const uint16_t* __restrict__ x, int64_t m, int64_t k, int64_t ldx,
                        uint8_t* __restrict__ codes, int64_t ld_codes, float* __restrict__ scales,
                        int64_t ssm, int64_t ssg, int groups, int native_half,
