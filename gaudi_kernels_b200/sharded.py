@@ -84,6 +84,8 @@ def reference_sharded(x_local, weight_local, scales_local, *, native_half=True, 
     activation matrix with its weight slice.  Returns this rank's [M, N / W] slice of the product, on the host
     when x_local is a host tensor (into `out` when given; a pinned tensor keeps the copy asynchronous until the
     final wait).  Results equal `reference()` on the same columns bit for bit: the quantization is row-local.
+    Every rank must pass the same number of rows (M is a multiple of the group size), and every rank makes the call:
+    it contains two all-gathers and one small all-reduce of the status bits.
     """
     from . import _lib
     from .block_fp8_gemm import _copy_stream, _workspaces, _WAIT_TIMEOUT_MSG, gemm_block_fp8
