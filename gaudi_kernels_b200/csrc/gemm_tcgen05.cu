@@ -142,7 +142,7 @@ gemm_block128_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   const uint32_t tmem_base = tail->tmem_base;
 
   if (warp >= kEpiWarps) {
-   ptx::setmaxnreg_dec<40>();
+   ptx::setmaxnreg_dec<24>();
    if (warp == kEpiWarps) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -186,7 +186,7 @@ gemm_block128_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     }
    }
   } else {
-    ptx::setmaxnreg_inc<232>();
+    ptx::setmaxnreg_inc<240>();
     // ------------------------------------------------------------------ epilogue / promotion
     // TMEM loads complete only at a wait that covers all of a thread's outstanding loads, so the
     // latency of one 32-column load is hidden behind the FMAs of the previous one (two register
