@@ -216,7 +216,8 @@ def test_gemm_many_tiles_persistent_loop(gk):
         assert float((out.double().cpu() - y64).abs().max()) / rms <= TOL, cap
 
 
-@pytest.mark.parametrize("m,k,n", [(256, 256, 256), (300, 384, 520), (1024, 1024, 2048), (130, 208, 257)])
+@pytest.mark.parametrize("m,k,n", [(256, 256, 256), (300, 384, 520), (1024, 1024, 2048), (130, 208, 257), (512, 640, 1032),
+                                   (129, 128, 168), (64, 1152, 3000)])
 def test_gemm_pair_schedule_matches_single_cta_schedule(gk, m, k, n):
     # the CTA-pair schedule (cluster of 2, tcgen05 cta_group::2) must reproduce the single-CTA schedule bit for bit
     x, w, s, b = _random_problem(m, k, n, seed=m + k + n, bias=True)
