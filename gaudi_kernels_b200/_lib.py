@@ -22,6 +22,7 @@ SIGNATURES = {
     "bfp8_version": (_int, []),
     "bfp8_error_string": (_c.c_char_p, [_int]),
     "bfp8_last_cuda_error": (_int, []),
+    "bfp8_set_weights_at_rest": (_int, [_int]),
     "bfp8_reencode_half": (_int, [_ptr, _ptr, _i64, _ptr, _ptr, _i64, _ptr, _ptr, _ptr]),
     "bfp8_validate_e4m3": (_int, [_ptr, _i64, _ptr, _i64, _ptr, _ptr]),
     "bfp8_quant_block128_f32": (_int, [_ptr, _i64, _i64, _i64, _ptr, _i64, _ptr, _int, _ptr]),

@@ -81,6 +81,15 @@ def new_status(device):
     return _status_buffer(device)
 
 
+def set_weights_at_rest(on):
+    """Tell the library whether the weight codes given to the decode-bucket GEMMs (M <= 128) are at rest, i.e. written
+    by nothing that is still in flight when a GEMM is enqueued (bfp8_set_weights_at_rest).  When they are, each GEMM
+    starts streaming its weight before the previous kernel of the stream has finished; results are unchanged.
+    Process-wide; returns the previous setting.  A serving process turns it on once its checkpoint is loaded and
+    the device synchronised, and off again around any in-place rewrite of a weight."""
+    return bool(_lib.load().bfp8_set_weights_at_rest(1 if on else 0))
+
+
 def gemm_block_fp8(a_codes, a_scales, w_codes, w_scales, bias=None, out=None, out_dtype=torch.bfloat16,
                    check=True, schedule=0, max_ctas=0, wait_limit_cycles=0, status=None):
     """out[i, j] = sum_g a_scales[i, g] * w_scales[j // 128, g] * <a_codes[i, g-block], w_codes[j, g-block]> (+ bias[j]).

@@ -29,6 +29,7 @@ int launch_gemm_channel(const uint8_t* a_codes, int64_t lda, const float* a_scal
                         int64_t m, int64_t n, int64_t k, uint32_t* status_dev, long long wait_limit, int max_ctas,
                         cudaStream_t st);
 size_t smallm_workspace_bytes(int64_t m, int64_t n, int max_ctas);
+int set_weights_at_rest(int on);
 bool smallm_supported(int64_t n);
 }
 
@@ -91,6 +92,8 @@ extern "C" int bfp8_gemm_block128(const uint8_t* a_codes, int64_t lda, const flo
   return bfp8_gemm_block128_ex(a_codes, lda, a_scales, ldsa, w_codes, ldw, w_scales, bias, out, out_dtype, ldo,
                                m, n, k, workspace, workspace_bytes, status_dev, stream, 0, 0, 0);
 }
+
+extern "C" int bfp8_set_weights_at_rest(int on) { return set_weights_at_rest(on); }
 
 extern "C" int bfp8_gemm_token_channel(const uint8_t* a_codes, int64_t lda, const float* a_scales,
                                        const uint8_t* w_codes, int64_t ldw, const float* w_scales,

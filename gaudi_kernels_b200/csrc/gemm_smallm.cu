@@ -102,6 +102,7 @@ struct Params {
   // slot push_rank of its receive area [push_world][push_rows][n]; push_world == 0 stores to `out` as usual
   int push_world, push_rank, push_rows;
   uint16_t* push_recv[8];
+  int w_early;             // the weight codes are at rest (bfp8_set_weights_at_rest): request them before griddep_wait
 };
 
 // Where activation row j of a bf16 result goes (column 0 of that row).
@@ -208,21 +209,47 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   // Everything above touches only this CTA's shared memory and TMEM, so under a programmatic dependent launch it
   // runs while the previous kernel of the stream is still finishing; from here on global memory is read and
   // written (activations and workspace may come from that kernel), so every thread waits for it first.
+  // The one exception is the weight matrix when the caller has declared it at rest (nothing in flight writes
+  // it): the producer then asks for the W half of as many units as the pipeline holds before the wait, so the
+  // stream from HBM is already running when the previous kernel drains.  Each stage's barrier expects the whole
+  // stage; the activation half follows after the wait.
   ptx::griddep_launch_dependents();
+  int early = 0;                                               // stages whose W half is already on its way
+  if (p.w_early != 0 && warp == kEpiWarps && lane == 0) {
+    const uint64_t w_policy = ptx::l2_policy_evict_first();
+    int tile = static_cast<int>(u0 / G), g = static_cast<int>(u0 % G);
+    for (long long u = u0; u < u1 && early < C::kStages; ++u, ++early) {
+      const uint32_t full = ptx::smem_u32(&tail->full[early]);
+      ptx::mbar_arrive_expect_tx(full, C::kStageBytes);
+      ptx::tma_load_2d_hint(smem_base + early * C::kStageBytes, &tmap_w, full, g * BK, tile * BN, w_policy);
+      if (++g == G) { g = 0; ++tile; }
+    }
+  }
   ptx::griddep_wait();
 
   if (warp == kEpiWarps) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
+      // Every byte of W is read exactly once per launch, by one CTA: its lines are marked as the first to leave
+      // L2.  With the default policy the stream pushed out what the neighbouring kernels of a decode step and the
+      // activation tiles (read by every CTA) keep there: a gate/up GEMM followed by a down GEMM at M = 64 took
+      // 67 us per pair instead of the 51 us the two take on their own.
+      const uint64_t w_policy = ptx::l2_policy_evict_first();
       uint32_t stage = 0, phase = 0;
       int tile = static_cast<int>(u0 / G), g = static_cast<int>(u0 % G);       // kept incrementally: no division per unit
       for (long long u = u0; u < u1; ++u) {
-        if (!ptx::mbar_wait(ptx::smem_u32(&tail->empty[stage]), phase ^ 1u, abort_flag, p.wait_limit)) break;
         const uint32_t full = ptx::smem_u32(&tail->full[stage]);
         const uint32_t w_dst = smem_base + stage * C::kStageBytes;
-        ptx::mbar_arrive_expect_tx(full, C::kStageBytes);
-        ptx::tma_load_2d(w_dst, &tmap_w, full, g * BK, tile * BN);
-        ptx::tma_load_2d(w_dst + kWBytes, &tmap_a, full, g * BK, 0);
+        if (early > 0) {
+          // first pass over the ring, W already requested: nothing to wait for, only the activation half is missing
+          --early;
+          ptx::tma_load_2d(w_dst + kWBytes, &tmap_a, full, g * BK, 0);
+        } else {
+          if (!ptx::mbar_wait(ptx::smem_u32(&tail->empty[stage]), phase ^ 1u, abort_flag, p.wait_limit)) break;
+          ptx::mbar_arrive_expect_tx(full, C::kStageBytes);
+          ptx::tma_load_2d_hint(w_dst, &tmap_w, full, g * BK, tile * BN, w_policy);
+          ptx::tma_load_2d(w_dst + kWBytes, &tmap_a, full, g * BK, 0);
+        }
         if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
         if (++g == G) { g = 0; ++tile; }
       }
@@ -603,24 +630,32 @@ size_t smallm_workspace_bytes(int64_t m, int64_t n, int max_ctas) {
 // Grid size: every CTA should stream the same number of 16 KB units, and as few CTAs as possible should
 // end inside a tile (each such end costs a partial-sum round trip through the workspace).  With no more
 // tiles than SMs every tile gets the same whole number of CTAs, so a CTA holds exactly one K range of one
-// tile; with more tiles than SMs the unit list is cut evenly over all SMs.
+// tile.  With more tiles than SMs there are two candidates: the unit list cut evenly over all SMs (every CTA
+// then ends inside a tile), or the smallest grid that gives every CTA the same number of whole tiles (224 tiles
+// on 148 SMs: 112 CTAs with two tiles each, no partial sums, a quarter of the SMs idle).  Which one is faster
+// depends on how much the idle SMs would have contributed, so both are priced with figures measured on B200:
+// the rate one CTA streams W at for each padded row count (the epilogue paces it as the row count grows), the
+// rate HBM delivers to all of them together, and the cost of the partial-sum round trip.
 int smallm_grid(int64_t tiles, int64_t groups, int sms, int mp) {
   const long long units = tiles * groups;
   if (units < sms) return static_cast<int>(units);
-  if (tiles > sms && mp >= 32) {
-    // More tiles than SMs and many activation rows: the partial sums of a tile that ends in two CTAs (two fp32
-    // tiles of mp x 128 through global memory, a counter, a read-back) cost more than leaving some SMs idle, so
-    // the grid is the smallest one that gives every CTA the same number of whole tiles where the tile count
-    // allows it (224 tiles on 148 SMs: 112 CTAs with two tiles each).
-    const int64_t waves = (tiles + sms - 1) / sms;
-    return static_cast<int>((tiles + waves - 1) / waves);
-  }
   if (tiles <= sms) {
     long long per_tile = sms / tiles;
     if (per_tile > groups) per_tile = groups;
     return static_cast<int>(tiles * per_tile);
   }
-  return sms;
+  const int64_t waves = (tiles + sms - 1) / sms;
+  const int64_t whole_grid = (tiles + waves - 1) / waves;
+  if (tiles % whole_grid != 0) return sms;                 // no grid of whole tiles with this many waves
+  const double per_cta_gbs = mp <= 16 ? 64.0 : mp <= 32 ? 44.0 : mp <= 64 ? 35.0 : 27.0;
+  const double round_trip_us = mp <= 16 ? 4.5 : mp <= 32 ? 11.0 : mp <= 64 ? 14.0 : 30.0;
+  const double hbm_gbs = 7200.0;                           // read-only stream, all SMs
+  const double unit_kb = kWBytes / 1e3;
+  const double whole_rate = per_cta_gbs * whole_grid < hbm_gbs ? per_cta_gbs : hbm_gbs / whole_grid;
+  const double even_rate = per_cta_gbs * sms < hbm_gbs ? per_cta_gbs * sms : hbm_gbs;
+  const double whole_us = static_cast<double>(waves * groups) * unit_kb / whole_rate;
+  const double even_us = static_cast<double>(units) * unit_kb / even_rate + round_trip_us;
+  return whole_us <= even_us ? static_cast<int>(whole_grid) : sms;
 }
 
 // CTAs per tile for the cluster form, or 0 when it does not apply: at most half as many tiles as SMs, a
@@ -632,6 +667,12 @@ int smallm_cluster_size(int64_t tiles, int64_t groups, int sms) {
   while (cs > groups) cs >>= 1;
   return cs >= 2 ? cs : 0;
 }
+
+// Process-wide promise of the caller that the weight codes given to the decode-bucket GEMMs are not written by
+// anything still in flight (bfp8_set_weights_at_rest).
+static std::atomic<int> g_weights_at_rest{0};
+
+int set_weights_at_rest(int on) { return g_weights_at_rest.exchange(on != 0 ? 1 : 0, std::memory_order_relaxed); }
 
 int launch_gemm_smallm(const uint8_t* a_codes, int64_t lda, const float* a_scales, int64_t ldsa,
                        const uint8_t* w_codes, int64_t ldw, const float* w_scales, const float* bias, void* out,
@@ -682,6 +723,7 @@ int launch_gemm_smallm(const uint8_t* a_codes, int64_t lda, const float* a_scale
     for (int o = 0; o < push->world; ++o) p.push_recv[o] = reinterpret_cast<uint16_t*>(const_cast<void*>(push->recv[o]));
   }
   p.cluster = max_ctas > 0 ? 0 : smallm_cluster_size(p.tiles, p.groups, sms);
+  p.w_early = g_weights_at_rest.load(std::memory_order_relaxed);
   if (inter > 0) return dispatch<true>(mp, tmap_w, tmap_a, p, grid, st);
   return dispatch<false>(mp, tmap_w, tmap_a, p, grid, st);
 }

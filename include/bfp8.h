@@ -11,8 +11,8 @@
  *     (BFP8_STATUS_* bits).  The caller zeroes it before the first call and reads it after
  *     synchronising; several calls may share one word.
  *   - The library's only mutable global state is caches of facts about the device (driver entry points, SM
- *     count, per-kernel shared-memory and cluster limits) and the fixed scratch of
- *     bfp8_gemm_block128_noalloc; calls are re-entrant and may be issued from several host threads on
+ *     count, per-kernel shared-memory and cluster limits), the switch of bfp8_set_weights_at_rest and the
+ *     fixed scratch of bfp8_gemm_block128_noalloc; calls are re-entrant and may be issued from several host threads on
  *     different streams (that one entry point excepted, see there).  The caches are keyed by device ordinal
  *     and are not rebuilt after cudaDeviceReset: a process that resets a device must not call the library
  *     on it again.
@@ -167,6 +167,18 @@ int bfp8_gemm_token_channel(const uint8_t* a_codes, int64_t lda, const float* a_
                             const uint8_t* w_codes, int64_t ldw, const float* w_scales,
                             const float* bias, void* out, int out_dtype, int64_t ldo,
                             int64_t m, int64_t n, int64_t k, uint32_t* status_dev, void* stream);
+
+/* Declares, for the whole process, whether the weight operands (w_codes) of the decode-bucket GEMMs (m <= 128:
+ * bfp8_gemm_block128, _ex, _swiglu, _push, _noalloc) are at rest.  These kernels are launched so that their
+ * set-up overlaps the end of the previous kernel of the stream, and normally touch no global memory until that
+ * kernel has finished.  With on != 0 the caller promises that no work still in flight when such a GEMM is
+ * enqueued writes its w_codes (weights were prepared at load time and the device was synchronised since); the
+ * kernel then requests the first weight tiles of every CTA before it waits for the previous kernel, so the
+ * stream from HBM does not pause between the kernels of a decode step.  Activations, scales, bias, workspace
+ * and output are still touched only after the wait, and results do not change.  Off by default; returns the
+ * previous setting.  The reference has no counterpart (its weights are bound to the graph at compile time,
+ * csrc/host/generic_fp8_glue.hpp:125-130). */
+int bfp8_set_weights_at_rest(int on);
 
 /* bfp8_gemm_block128 for callers that cannot allocate a workspace where they make the call (for
  * example a server that handed all device memory to its own pools at start-up, or host code running
