@@ -252,6 +252,22 @@ def bench_codec(torch, lib, device, steps, warmup):
                                                            None, stream)) for i in range(len(xs))])
     nbytes = m * k * 3 + m * 4
     out["quantize_act_token"] = {"ms": ms, "bytes": nbytes, "gbs": nbytes / ms / 1e6, "shape": "bf16 [8192, 4096]"}
+    # the two activation quantizers on the activation of the multi-GPU workload (a launch of [8192, 4096] lasts about
+    # 20 us, of which the ramp at either end is a visible part)
+    del xs, xc
+    m, k = WORKLOADS["ffn70b"][0], WORKLOADS["ffn70b"][1]
+    xs = [torch.randn((m, k), generator=g, device=device).to(torch.bfloat16) for _ in range(3)]
+    xc = [torch.empty((m, k), dtype=torch.uint8, device=device) for _ in range(3)]
+    xsc = torch.empty((k // 128, m), dtype=torch.float32, device=device)
+    tsc = torch.empty(m, dtype=torch.float32, device=device)
+    ms = timed([(lambda i=i: lib.bfp8_quant_act_1x128_bf16(xs[i].data_ptr(), m, k, k, xc[i].data_ptr(), k, xsc.data_ptr(), 1, m, 1,
+                                                           None, stream)) for i in range(len(xs))])
+    nbytes = m * k * 3 + (k // 128) * m * 4
+    out["quantize_act_1x128_16384x8192"] = {"ms": ms, "bytes": nbytes, "gbs": nbytes / ms / 1e6, "shape": "bf16 [16384, 8192]"}
+    ms = timed([(lambda i=i: lib.bfp8_quant_act_token_bf16(xs[i].data_ptr(), m, k, k, xc[i].data_ptr(), k, tsc.data_ptr(), 1,
+                                                           None, stream)) for i in range(len(xs))])
+    nbytes = m * k * 3 + m * 4
+    out["quantize_act_token_16384x8192"] = {"ms": ms, "bytes": nbytes, "gbs": nbytes / ms / 1e6, "shape": "bf16 [16384, 8192]"}
     return out
 
 

@@ -478,54 +478,60 @@ quant_act_token_warp_kernel(const uint16_t* __restrict__ x, int64_t m, int64_t k
   }
 }
 
-// Rows of up to 4096 columns, second form: 128 threads per row (two rows per CTA), four 16-byte loads per thread,
-// the row maximum combined through shared memory and a 128-thread named barrier.  Fewer registers than the
-// warp-per-row form, so four times as many warps are resident and hide the load latency.
-constexpr int kTokHalfThreads = 128;
-constexpr int kTokHalfVecs = 4;
-constexpr int kTokHalfMaxK = kTokHalfVecs * kTokHalfThreads * 8;     // 4096
+// Many rows of up to 8192 columns: kRowThreads threads per row (32, 64, 128 or 256, the smallest that covers the row
+// with four 16-byte loads per thread), 256 / kRowThreads rows per CTA, the row maximum combined through shared memory
+// and a named barrier of the row's threads.  Fewer registers than the warp-per-row form, so four times as many warps
+// are resident and hide the load latency; sizing the thread group to the row keeps every thread loaded.
+constexpr int kTokGroupCta = 256;
+constexpr int kTokGroupVecs = 4;
+constexpr int kTokGroupMaxK = kTokGroupVecs * kTokGroupCta * 8;      // 8192
 
-__global__ void __launch_bounds__(2 * kTokHalfThreads, 4)
-quant_act_token_half_kernel(const uint16_t* __restrict__ x, int64_t m, int64_t k, int64_t ldx,
-                            uint8_t* __restrict__ codes, int64_t ld_codes, float* __restrict__ scales,
-                            int native_half, uint32_t* __restrict__ status) {
-  __shared__ float warp_max[2][kTokHalfThreads / 32];
-  const int half = threadIdx.x / kTokHalfThreads;                  // which of the CTA's two rows
-  const int t = threadIdx.x - half * kTokHalfThreads;
-  const int64_t row = static_cast<int64_t>(blockIdx.x) * 2 + half;
+template <int kRowThreads>
+__global__ void __launch_bounds__(kTokGroupCta, 4)
+quant_act_token_group_kernel(const uint16_t* __restrict__ x, int64_t m, int64_t k, int64_t ldx,
+                             uint8_t* __restrict__ codes, int64_t ld_codes, float* __restrict__ scales,
+                             int native_half, uint32_t* __restrict__ status) {
+  constexpr int kRows = kTokGroupCta / kRowThreads;                // rows per CTA
+  constexpr int kWarps = kRowThreads / 32;                         // warps per row
+  __shared__ float warp_max[kRows][kWarps];
+  const int grp = threadIdx.x / kRowThreads;                       // which of the CTA's rows
+  const int t = threadIdx.x - grp * kRowThreads;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * kRows + grp;
   const bool row_ok = row < m;
   const uint4* xrow = reinterpret_cast<const uint4*>(x + (row_ok ? row : 0) * ldx);
   uint2* crow = reinterpret_cast<uint2*>(codes + (row_ok ? row : 0) * ld_codes);
   const int nvec = row_ok ? static_cast<int>(k >> 3) : 0;
-  uint4 raw[kTokHalfVecs];
+  uint4 raw[kTokGroupVecs];
 #pragma unroll
-  for (int u = 0; u < kTokHalfVecs; ++u) {
-    const int i = u * kTokHalfThreads + t;
+  for (int u = 0; u < kTokGroupVecs; ++u) {
+    const int i = u * kRowThreads + t;
     raw[u] = make_uint4(0u, 0u, 0u, 0u);
     if (i < nvec) raw[u] = __ldcs(xrow + i);
   }
   float amax = 0.0f;
 #pragma unroll
-  for (int u = 0; u < kTokHalfVecs; ++u) {
+  for (int u = 0; u < kTokGroupVecs; ++u) {
     const uint32_t* r = reinterpret_cast<const uint32_t*>(&raw[u]);
 #pragma unroll
     for (int j = 0; j < 4; ++j) amax = max_abs_nan(max_abs_nan(amax, bf16_lo_to_float(r[j])), bf16_hi_to_float(r[j]));
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) amax = max_abs_nan(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-  if ((t & 31) == 0) warp_max[half][t >> 5] = amax;
-  asm volatile("bar.sync %0, %1;" ::"r"(1 + half), "r"(kTokHalfThreads) : "memory");
-  amax = warp_max[half][0];
+  if (kWarps > 1) {
+    if ((t & 31) == 0) warp_max[grp][t >> 5] = amax;
+    asm volatile("bar.sync %0, %1;" ::"r"(1 + grp), "r"(kRowThreads) : "memory");
+    amax = warp_max[grp][0];
 #pragma unroll
-  for (int i = 1; i < kTokHalfThreads / 32; ++i) amax = max_abs_nan(amax, warp_max[half][i]);
+    for (int i = 1; i < kWarps; ++i) amax = max_abs_nan(amax, warp_max[grp][i]);
+  }
   if (row_ok && !(amax < __int_as_float(0x7f800000)) && t == 0 && status != nullptr)
     atomicOr(status, BFP8_STATUS_NONFINITE_INPUT);
   const float s = __fdiv_rn(amax == 0.0f ? 1.0f : amax, 448.0f);
   const float rcp = __frcp_rn(s);
   if (row_ok && t == 0) scales[row] = native_half ? __fmul_rn(s, 2.0f) : s;
 #pragma unroll
-  for (int u = 0; u < kTokHalfVecs; ++u) {
-    const int i = u * kTokHalfThreads + t;
+  for (int u = 0; u < kTokGroupVecs; ++u) {
+    const int i = u * kRowThreads + t;
     const uint32_t* r = reinterpret_cast<const uint32_t*>(&raw[u]);
     float f[8];
 #pragma unroll
@@ -775,10 +781,21 @@ extern "C" int bfp8_quant_act_token_bf16(const uint16_t* x, int64_t m, int64_t k
   if (m <= 0 || k <= 0 || ldx < k || ld_codes < k || m > 2147483647LL) return BFP8_ERR_SHAPE;
   if (!aligned(x, 2) || !aligned(scales, 4)) return BFP8_ERR_ALIGN;
   const int vec = aligned(x, 16) && aligned(codes, 8) && ldx % 8 == 0 && ld_codes % 8 == 0 && k % 8 == 0;
-  if (vec && k <= kTokHalfMaxK && m >= 4LL * sm_count()) {
-    quant_act_token_half_kernel<<<static_cast<int>((m + 1) / 2), 2 * kTokHalfThreads, 0,
-                                  static_cast<cudaStream_t>(stream)>>>(x, m, k, ldx, codes, ld_codes, scales,
-                                                                       native_half, status_dev);
+  if (vec && k <= kTokGroupMaxK && m >= 4LL * sm_count()) {
+    const cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int vecs = static_cast<int>(k >> 3);
+    if (vecs <= 32 * kTokGroupVecs)
+      quant_act_token_group_kernel<32><<<static_cast<int>((m + 7) / 8), kTokGroupCta, 0, st>>>(
+          x, m, k, ldx, codes, ld_codes, scales, native_half, status_dev);
+    else if (vecs <= 64 * kTokGroupVecs)
+      quant_act_token_group_kernel<64><<<static_cast<int>((m + 3) / 4), kTokGroupCta, 0, st>>>(
+          x, m, k, ldx, codes, ld_codes, scales, native_half, status_dev);
+    else if (vecs <= 128 * kTokGroupVecs)
+      quant_act_token_group_kernel<128><<<static_cast<int>((m + 1) / 2), kTokGroupCta, 0, st>>>(
+          x, m, k, ldx, codes, ld_codes, scales, native_half, status_dev);
+    else
+      quant_act_token_group_kernel<256><<<static_cast<int>(m), kTokGroupCta, 0, st>>>(
+          x, m, k, ldx, codes, ld_codes, scales, native_half, status_dev);
   } else if (vec && k <= kTokWarpMaxK) {
     const int rows_per_cta = kTokWarpThreads / 32;
     quant_act_token_warp_kernel<<<static_cast<int>((m + rows_per_cta - 1) / rows_per_cta), kTokWarpThreads, 0,

@@ -20,7 +20,9 @@ def gk():
 
 
 @pytest.mark.parametrize("shape", [(1, 128), (37, 384), (5, 200), (3, 1000), (64, 4096), (16, 14336), (2, 20480), (7, 130),
-                                   (1024, 4096), (701, 384), (600, 200)])     # many rows: two rows per CTA
+                                   # many rows: thread groups of 128, 32, 32, 64, 64, 256 and 256 threads per row
+                                   (1024, 4096), (701, 384), (600, 200), (650, 1536), (597, 2048), (600, 8192),
+                                   (640, 5000)])
 @pytest.mark.parametrize("half", [True, False])
 def test_token_quantizer_matches_restatement(gk, shape, half):
     g = torch.Generator().manual_seed(shape[0] * 5 + shape[1])
