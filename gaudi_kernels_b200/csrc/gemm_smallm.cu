@@ -75,7 +75,6 @@ struct SmemTail {
   uint64_t empty[kMaxStages];
   uint64_t tmem_full[kAccBufs];
   uint64_t tmem_empty[kAccBufs];
-  uint64_t scale_full[kAccBufs];
   float scale[kAccBufs][128];        // sa[g, 0..MP) * sw[tile, g] of the unit in each TMEM buffer
   float scale_up[kAccBufs][128];     // SwiGLU form: the same with the up block's weight scale (lanes 64-127)
   uint32_t tmem_base;
@@ -187,9 +186,10 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
       ptx::mbar_init(ptx::smem_u32(&tail->empty[s]), 1);
     }
     for (int b = 0; b < kAccBufs; ++b) {
-      ptx::mbar_init(ptx::smem_u32(&tail->tmem_full[b]), 1);
+      // a buffer is ready for the epilogue when its MMAs have completed (tcgen05.commit) and the scale loader has
+      // parked the unit's scale products next to it: two arrivals on one barrier, one poll per unit for the epilogue
+      ptx::mbar_init(ptx::smem_u32(&tail->tmem_full[b]), 2);
       ptx::mbar_init(ptx::smem_u32(&tail->tmem_empty[b]), kEpiWarps);
-      ptx::mbar_init(ptx::smem_u32(&tail->scale_full[b]), 1);
     }
     tail->abort_flag = 0;
     ptx::fence_mbar_init();
@@ -322,7 +322,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
                 if (swiglu) tail->scale_up[buf][lane + 32 * q] = va[i][q] * vu[kSwiGLU ? i : 0];
               }
             __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&tail->scale_full[buf]));
+            if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&tail->tmem_full[buf]));
             if (u + kScaleAhead < u1) fetch(va[i], vw[i], vu[kSwiGLU ? i : 0]);
             ++kb;
           }
@@ -420,8 +420,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
       const uint32_t buf = kb % kAccBufs, acc_phase = (kb / kAccBufs) & 1u;
       // uniform across the warp before the warp-collective TMEM loads
       ok = __all_sync(0xffffffffu,
-                      ptx::mbar_wait(ptx::smem_u32(&tail->tmem_full[buf]), acc_phase, abort_flag, p.wait_limit) &&
-                      ptx::mbar_wait(ptx::smem_u32(&tail->scale_full[buf]), acc_phase, abort_flag, p.wait_limit));
+                      ptx::mbar_wait(ptx::smem_u32(&tail->tmem_full[buf]), acc_phase, abort_flag, p.wait_limit));
       if (!ok) break;
       ptx::tc_fence_after_sync();
       const uint32_t taddr = tmem_base + lane_addr + buf * MP;
@@ -440,15 +439,20 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         ptx::tmem_wait_ld16(r[0]);
 #pragma unroll
         for (int c = 1; c < kChunk / 16; ++c) ptx::tmem_regs_ready16(r[c]);
+        if (h == MP / kChunk - 1) {
+          // every column of the unit and its scales are in registers: the buffer (and the scale slot beside it) goes
+          // back before the FMAs are issued, so the barrier operation completes under the arithmetic instead of in
+          // front of the next unit's poll
+          ptx::tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&tail->tmem_empty[buf]));
+        }
 #pragma unroll
         for (int c = 0; c < kChunk / 16; ++c)
 #pragma unroll
           for (int j = 0; j < 16; ++j)
             acc[h * kChunk + c * 16 + j] = fmaf(__uint_as_float(r[c][j]), s[c * 16 + j], acc[h * kChunk + c * 16 + j]);
       }
-      ptx::tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&tail->tmem_empty[buf]));
       if (!kCluster && (g == G - 1 || u == u1 - 1)) segment_end(true);
     }
     if (!kCluster && !ok) {
