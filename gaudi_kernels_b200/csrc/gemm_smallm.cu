@@ -20,9 +20,10 @@
 // Each K block is accumulated from zero into one of four small TMEM buffers and folded into register
 // accumulators with its scale product sa[g, i] * sw[j/128, g], as in the large-tile schedule.
 //
-// Warp roles (256 threads): warps 0-3 epilogue (thread = weight row), warp 4 TMA producer, warp 5
-// TMEM owner and MMA issuer of the even units, warp 7 MMA issuer of the odd units (issuing a unit's four
-// MMAs and its two commits takes one thread longer than the unit's HBM time, so two threads alternate),
+// Warp roles (320 threads; 256 with 64 or 128 activation columns): warps 0-3 epilogue (thread = weight row), warp 4
+// TMA producer, warp 5 TMEM owner and first MMA issuer, warps 7-9 (7 alone in the 256-thread form) the other MMA
+// issuers - a thread that has issued a unit's four MMAs and its two commits is held until the MMAs have
+// completed, several times the unit's HBM time, so the issuers take the units in turn -
 // warp 6 scale loader: it fetches the scale products of the units ahead
 // (global-memory latency is far longer than a unit's 16 KB of HBM time) and parks them in a small
 // shared-memory ring next to the TMEM buffers.  All barrier waits are bounded.
@@ -52,7 +53,6 @@ namespace {
 constexpr int BN = 128;            // weight rows per tile = one scale block
 constexpr int BK = 128;
 constexpr int kEpiWarps = 4;
-constexpr int kThreads = (kEpiWarps + 4) * 32;
 constexpr int kScaleAhead = 8;     // units whose scales are in flight in the loader's registers
 constexpr int kAccBufs = 4;
 constexpr int kWBytes = BN * BK;   // 16 KB of W per unit
@@ -67,7 +67,15 @@ struct Cfg {
   static constexpr int kStageBytes = kWBytes + kABytes;
   static constexpr int kStages = (kSmemBudget / kStageBytes) < kMaxStages ? (kSmemBudget / kStageBytes) : kMaxStages;
   static constexpr int kTmemCols = (kAccBufs * MP) < 32 ? 32 : (kAccBufs * MP);
-  static_assert(kStages % 2 == 0 && kAccBufs % 2 == 0, "the two MMA issuers alternate over stages and TMEM buffers");
+  // A thread that issues a unit's MMAs and commits is held until those MMAs have completed, far longer than a unit's
+  // HBM time (about 1 300 cycles per unit at 64 activation columns), so several threads take the units in turn:
+  // four of them up to 32 activation columns, two beyond: with 64 columns four measured slower than two (16.8 against
+  // 15.4 us at K=4096, N=14336 - the extra warps share their schedulers with epilogue warps that now have real
+  // work), and with 128 the epilogue needs the registers a larger CTA would take away.
+  static constexpr int kIssuers = MP <= 32 ? 4 : 2;
+  static constexpr int kThreads = (kEpiWarps + 2 + kIssuers) * 32;
+  static_assert(kIssuers <= kAccBufs && kAccBufs % kIssuers == 0 && kIssuers < kStages,
+                "issuer i owns TMEM buffers i, i + kIssuers, ... and steps through the stage ring by kIssuers");
 };
 
 struct SmemTail {
@@ -156,7 +164,7 @@ __host__ __device__ inline int cta_of_unit(long long u, long long total, long lo
 }
 
 template <int MP, bool kCluster, bool kSwiGLU>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(Cfg<MP>::kThreads, 1)
 gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a,
                    const Params p) {
   using C = Cfg<MP>;
@@ -254,13 +262,13 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         if (++g == G) { g = 0; ++tile; }
       }
     }
-  } else if (warp == kEpiWarps + 1 || warp == kEpiWarps + 3) {
-    // ------------------------------------------------------------------ MMA issuers (even / odd units)
+  } else if (warp == kEpiWarps + 1 || warp >= kEpiWarps + 3) {
+    // ------------------------------------------------------------------ MMA issuers (units first, first + kIssuers, ...)
     if (lane == 0) {
       constexpr uint32_t idesc = ptx::umma_idesc_e4m3(BN, MP);
-      const uint32_t first = warp == kEpiWarps + 1 ? 0u : 1u;
-      uint32_t stage = first % C::kStages, phase = 0, kb = first;
-      for (long long u = u0 + first; u < u1; u += 2, kb += 2) {
+      const uint32_t first = warp == kEpiWarps + 1 ? 0u : static_cast<uint32_t>(warp - (kEpiWarps + 2));   // 0, 1, 2, 3
+      uint32_t stage = first, phase = 0, kb = first;
+      for (long long u = u0 + first; u < u1; u += C::kIssuers, kb += C::kIssuers) {
         const uint32_t buf = kb % kAccBufs, acc_phase = (kb / kAccBufs) & 1u;
         if (!ptx::mbar_wait(ptx::smem_u32(&tail->tmem_empty[buf]), acc_phase ^ 1u, abort_flag, p.wait_limit)) break;
         if (!ptx::mbar_wait(ptx::smem_u32(&tail->full[stage]), phase, abort_flag, p.wait_limit)) break;
@@ -274,7 +282,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
           ptx::umma_f8(d, w_desc + 2u * k4, a_desc + 2u * k4, idesc, k4 > 0);
         ptx::umma_commit(ptx::smem_u32(&tail->empty[stage]));
         ptx::umma_commit(ptx::smem_u32(&tail->tmem_full[buf]));
-        stage += 2;
+        stage += C::kIssuers;
         if (stage >= C::kStages) { stage -= C::kStages; phase ^= 1u; }
       }
     }
@@ -540,7 +548,7 @@ int launch(const CUtensorMap& tmap_w, const CUtensorMap& tmap_a, const Params& p
   // launched so that the set-up of this kernel may overlap the tail of the previous kernel in the stream
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
-  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.blockDim = dim3(C::kThreads, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
@@ -564,7 +572,7 @@ int launch_clustered(const CUtensorMap& tmap_w, const CUtensorMap& tmap_a, const
   if (rc != BFP8_OK) return rc;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(p.tiles * p.cluster), 1, 1);
-  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.blockDim = dim3(C::kThreads, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
   cudaLaunchAttribute attr[2];
