@@ -268,6 +268,16 @@ def bench_codec(torch, lib, device, steps, warmup):
                                                            None, stream)) for i in range(len(xs))])
     nbytes = m * k * 3 + m * 4
     out["quantize_act_token_16384x8192"] = {"ms": ms, "bytes": nbytes, "gbs": nbytes / ms / 1e6, "shape": "bf16 [16384, 8192]"}
+    # the re-encode on the 70B-class weight [28672, 8192] (235 MB each way; the [8192, 8192] launch above lasts 25 us)
+    del xs, xc
+    wn, wk = WORKLOADS["ffn70b"][2], WORKLOADS["ffn70b"][1]
+    wsrc = [torch.randint(0, 0x7f, (wn, wk), generator=g, device=device, dtype=torch.uint8) for _ in range(3)]
+    wdst = [torch.empty((wn, wk), dtype=torch.uint8, device=device) for _ in range(3)]
+    wsc = torch.rand((wn // 128, wk // 128), generator=g, device=device) + 0.01
+    wsc2 = torch.empty_like(wsc)
+    ms = timed([(lambda i=i: lib.bfp8_reencode_half(wsrc[i].data_ptr(), wdst[i].data_ptr(), wn * wk, wsc.data_ptr(), wsc2.data_ptr(),
+                                                    wsc.numel(), status.data_ptr(), status.data_ptr() + 8, stream)) for i in range(3)])
+    out["reencode_half_28672x8192"] = {"ms": ms, "bytes": wn * wk * 2, "gbs": wn * wk * 2 / ms / 1e6, "shape": "e4m3 [28672, 8192]"}
     return out
 
 
