@@ -7,10 +7,11 @@
 //   * the work is cut into units of (128 weight rows) x (one 128-wide K block) = 16 KB of W, and the
 //     unit list - tile-major, K-block-minor - is split evenly over the CTAs (stream-K), so every SM
 //     streams the same number of bytes whatever N and K are;
-//   * a CTA that finishes only part of a tile's K range writes its fp32 partial to the workspace; the
-//     last CTA to arrive at a tile (per-tile counter) adds the partials in CTA order - a fixed order,
-//     so results do not depend on timing - applies the bias and stores the tile.  Counters are
-//     returned to zero, so a zero-initialised workspace stays reusable.
+//   * a tile whose K range is spread over several CTAs is finished by the first of them: the others write
+//     their fp32 partials to the workspace and count themselves in (per-tile counter); the first CTA, whose
+//     part of the tile is the last thing it works on, waits (bounded) for the count, adds the partials to
+//     its own sums in CTA order - a fixed order, so results do not depend on timing - applies the bias and
+//     stores the tile.  Counters are returned to zero, so a zero-initialised workspace stays reusable.
 // When there are at most half as many tiles as SMs, the CTAs that share a tile form a thread-block cluster
 // (2, 4 or 8 CTAs, each with an equal slice of the K range) and exchange their partials through distributed
 // shared memory instead: every CTA owns MP / cluster-size of the padded activation rows, receives those rows
@@ -355,8 +356,19 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     // thread whose bounded wait expired still calls this for every remaining segment end (alive == false: it takes
     // part in the barriers and the counter protocol, stores nothing), see the loop after the main one.
     long long u = u0;
+    int pending_tile = -1;                                     // tile whose partial is stored but not yet counted in
+    // makes this CTA's partial of tile t visible and counts the CTA in at that tile (all 128 epilogue threads)
+    auto count_in = [&](int t) {
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (epi_tid == 0) atomicAdd(p.counters + t, 1u);
+    };
     auto segment_end = [&](bool alive) {
         // ---- end of this CTA's segment of the tile
+        if (u == u1 - 1 && pending_tile >= 0) {                  // last segment: settle what the first one left open
+          count_in(pending_tile);
+          pending_tile = -1;
+        }
         const long long tile_first = static_cast<long long>(tile) * G;
         const int c_first = cta_of_unit(tile_first, p.total_units, parts);
         const int c_last = cta_of_unit(tile_first + G - 1, p.total_units, parts);
@@ -364,34 +376,48 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         const bool whole = (seg_start == tile_first) && (g == G - 1);
         bool do_store = whole;
         if (!whole) {
-          // partial slot: 0 if this tile is the CTA's first, else 1
-          const int slot = (static_cast<long long>(tile) == u0 / G) ? 0 : 1;
-          float* dst = p.partials + (static_cast<int64_t>(blockIdx.x) * 2 + slot) * (MP * BN);
+          // The tile's first CTA finishes it.  Its segment is the last thing it does, while the CTAs after it met the
+          // tile at the start of their ranges, so their partial sums are normally waiting for it: they store them,
+          // fence and count themselves in; the first CTA waits (bounded) for the count, adds the partials to its own
+          // registers in CTA order - which is K order, a fixed order, and (0 + own) + p1 + ... is what a sum over
+          // stored partials starting from zero gives bit for bit - and stores the tile.  One trip through L2 for
+          // the finisher instead of the store / fence / count / read-back chain of a last-arriver scheme.
+          // A CTA that meets such a tile at the start of its range only stores its partial there and carries on;
+          // the fence and the count follow at its last segment end (count_in), where nothing is left to stall.
+          const uint32_t others = static_cast<uint32_t>(c_last - c_first);
+          if (static_cast<int>(blockIdx.x) != c_first) {
+            // partial slot: 0 if this tile is the CTA's first, else 1
+            const int slot = (static_cast<long long>(tile) == u0 / G) ? 0 : 1;
+            float* dst = p.partials + (static_cast<int64_t>(blockIdx.x) * 2 + slot) * (MP * BN);
 #pragma unroll
-          for (int j = 0; j < MP; ++j) dst[j * BN + wrow] = acc[j];
-          __threadfence();
-          asm volatile("bar.sync 1, 128;" ::: "memory");
-          if (epi_tid == 0) {
-            const uint32_t prev = atomicAdd(p.counters + tile, 1u);
-            const uint32_t nseg = static_cast<uint32_t>(c_last - c_first + 1);
-            tail->last_flag = (prev == nseg - 1) ? 1u : 0u;
-            if (prev == nseg - 1) p.counters[tile] = 0;          // leave the workspace reusable
-          }
-          asm volatile("bar.sync 1, 128;" ::: "memory");
-          do_store = tail->last_flag != 0;
-          if (do_store) {
-            __threadfence();
-#pragma unroll
-            for (int j = 0; j < MP; ++j) acc[j] = 0.0f;
-            for (int c = c_first; c <= c_last; ++c) {              // fixed order: results are run-to-run identical
-              const int cslot = (static_cast<long long>(tile) == first_unit(c, p.total_units, parts) / G) ? 0 : 1;
-              const float* src = p.partials + (static_cast<int64_t>(c) * 2 + cslot) * (MP * BN);
-#pragma unroll
-              for (int j = 0; j < MP; ++j)
-                if (j < p.m) acc[j] += __ldcg(src + j * BN + wrow);
+            for (int j = 0; j < MP; ++j) dst[j * BN + wrow] = acc[j];
+            if (u == u1 - 1) count_in(tile);
+            else pending_tile = tile;
+          } else {
+            if (epi_tid == 0) {
+              uint32_t arrived = 1u;
+              const long long t0 = clock64();
+              while (ptx::ld_acquire_gpu_u32(p.counters + tile) != others) {
+                if (*abort_flag != 0) { arrived = 0u; break; }
+                if (clock64() - t0 > p.wait_limit) { *abort_flag = 1; arrived = 0u; break; }
+              }
+              if (arrived != 0u) p.counters[tile] = 0;            // leave the workspace reusable
+              tail->last_flag = arrived;
             }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            do_store = tail->last_flag != 0;
+            if (do_store) {
+              __threadfence();
+              for (int c = c_first + 1; c <= c_last; ++c) {        // fixed order: results are run-to-run identical
+                const int cslot = (static_cast<long long>(tile) == first_unit(c, p.total_units, parts) / G) ? 0 : 1;
+                const float* src = p.partials + (static_cast<int64_t>(c) * 2 + cslot) * (MP * BN);
+#pragma unroll
+                for (int j = 0; j < MP; ++j)
+                  if (j < p.m) acc[j] += __ldcg(src + j * BN + wrow);
+              }
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");        // last_flag may be rewritten next segment
           }
-          asm volatile("bar.sync 1, 128;" ::: "memory");          // last_flag may be rewritten next segment
         }
         if (kSwiGLU) {
           // SwiGLU form: do_store is the same for all 128 threads, so the barriers inside are safe
@@ -660,7 +686,7 @@ int smallm_grid(int64_t tiles, int64_t groups, int sms, int mp) {
   const int64_t whole_grid = (tiles + waves - 1) / waves;
   if (tiles % whole_grid != 0) return sms;                 // no grid of whole tiles with this many waves
   const double per_cta_gbs = mp <= 16 ? 64.0 : mp <= 32 ? 44.0 : mp <= 64 ? 35.0 : 27.0;
-  const double round_trip_us = mp <= 16 ? 4.5 : mp <= 32 ? 11.0 : mp <= 64 ? 14.0 : 30.0;
+  const double round_trip_us = mp <= 16 ? 3.0 : mp <= 32 ? 5.0 : mp <= 64 ? 6.5 : 11.5;
   const double hbm_gbs = 7200.0;                           // read-only stream, all SMs
   const double unit_kb = kWBytes / 1e3;
   const double whole_rate = per_cta_gbs * whole_grid < hbm_gbs ? per_cta_gbs : hbm_gbs / whole_grid;
