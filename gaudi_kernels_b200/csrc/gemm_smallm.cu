@@ -685,7 +685,7 @@ int smallm_grid(int64_t tiles, int64_t groups, int sms, int mp) {
   const int64_t waves = (tiles + sms - 1) / sms;
   const int64_t whole_grid = (tiles + waves - 1) / waves;
   if (tiles % whole_grid != 0) return sms;                 // no grid of whole tiles with this many waves
-  const double per_cta_gbs = mp <= 16 ? 64.0 : mp <= 32 ? 44.0 : mp <= 64 ? 35.0 : 27.0;
+  const double per_cta_gbs = mp <= 16 ? 64.0 : mp <= 32 ? 53.0 : mp <= 64 ? 44.0 : 27.0;
   const double round_trip_us = mp <= 16 ? 3.0 : mp <= 32 ? 5.0 : mp <= 64 ? 6.5 : 11.5;
   const double hbm_gbs = 7200.0;                           // read-only stream, all SMs
   const double unit_kb = kWBytes / 1e3;
