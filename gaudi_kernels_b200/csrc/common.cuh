@@ -27,6 +27,40 @@ inline int cuda_fail(cudaError_t e) {
 
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 
+// Optional in-kernel timeline, for the diagnostic build only (-DBFP8_TIMELINE, written to libbfp8_timeline.so by
+// `python -m gaudi_kernels_b200.build --timeline`).  The GEMM kernels then stamp %clock at a few events of every
+// unit of work into a shared-memory log, and one CTA copies its log to a device array at teardown, which a
+// bfp8_timeline_read_* function of the same file returns.  In the product build the macros expand to nothing.
+#ifdef BFP8_TIMELINE
+constexpr int kTimelineEvents = 8;      // events per unit of work
+constexpr int kTimelineUnits = 40;      // units of work logged (the CTA's first ones; the large-tile kernel has 1.9 KB of shared memory to spare)
+constexpr int kTimelineCta = 5;         // the CTA whose log is kept
+__device__ __forceinline__ unsigned int timeline_clock() {
+  unsigned int t;
+  asm volatile("mov.u32 %0, %%clock;" : "=r"(t));
+  return t;
+}
+#define BFP8_TL_DECL                                                                                          \
+  __shared__ unsigned int tl_log[::bfp8::kTimelineEvents][::bfp8::kTimelineUnits];                            \
+  for (int tl_i_ = threadIdx.x; tl_i_ < ::bfp8::kTimelineEvents * ::bfp8::kTimelineUnits; tl_i_ += blockDim.x) \
+    (&tl_log[0][0])[tl_i_] = 0u;   /* made visible by the kernel's first __syncthreads */
+#define BFP8_TL(event, unit)                                                                    \
+  do {                                                                                          \
+    const long long tl_u_ = static_cast<long long>(unit);                                       \
+    if (tl_u_ >= 0 && tl_u_ < ::bfp8::kTimelineUnits) tl_log[event][tl_u_] = ::bfp8::timeline_clock(); \
+  } while (0)
+#define BFP8_TL_DUMP(dst)                                                                                     \
+  do {                                                                                                        \
+    if (blockIdx.x == ::bfp8::kTimelineCta)                                                                   \
+      for (int tl_i_ = threadIdx.x; tl_i_ < ::bfp8::kTimelineEvents * ::bfp8::kTimelineUnits; tl_i_ += blockDim.x) \
+        (dst)[tl_i_] = (&tl_log[0][0])[tl_i_];                                                                \
+  } while (0)
+#else
+#define BFP8_TL_DECL
+#define BFP8_TL(event, unit) ((void)0)
+#define BFP8_TL_DUMP(dst) ((void)0)
+#endif
+
 // Number of SMs of the current device (cached per device id).
 int sm_count();
 

@@ -51,6 +51,10 @@ struct SmallPush {
 
 namespace {
 
+#ifdef BFP8_TIMELINE
+__device__ unsigned int g_timeline_smallm[kTimelineEvents * kTimelineUnits];
+#endif
+
 constexpr int BN = 128;            // weight rows per tile = one scale block
 constexpr int BK = 128;
 constexpr int kEpiWarps = 4;
@@ -169,6 +173,7 @@ __global__ void __launch_bounds__(Cfg<MP>::kThreads, 1)
 gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a,
                    const Params p) {
   using C = Cfg<MP>;
+  BFP8_TL_DECL
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
@@ -255,6 +260,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
           ptx::tma_load_2d(w_dst + kWBytes, &tmap_a, full, g * BK, 0);
         } else {
           if (!ptx::mbar_wait(ptx::smem_u32(&tail->empty[stage]), phase ^ 1u, abort_flag, p.wait_limit)) break;
+          BFP8_TL(0, u - u0);                                   // stage free, copies issued
           ptx::mbar_arrive_expect_tx(full, C::kStageBytes);
           ptx::tma_load_2d_hint(w_dst, &tmap_w, full, g * BK, tile * BN, w_policy);
           ptx::tma_load_2d(w_dst + kWBytes, &tmap_a, full, g * BK, 0);
@@ -272,7 +278,9 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
       for (long long u = u0 + first; u < u1; u += C::kIssuers, kb += C::kIssuers) {
         const uint32_t buf = kb % kAccBufs, acc_phase = (kb / kAccBufs) & 1u;
         if (!ptx::mbar_wait(ptx::smem_u32(&tail->tmem_empty[buf]), acc_phase ^ 1u, abort_flag, p.wait_limit)) break;
+        BFP8_TL(1, u - u0);                                     // TMEM buffer free
         if (!ptx::mbar_wait(ptx::smem_u32(&tail->full[stage]), phase, abort_flag, p.wait_limit)) break;
+        BFP8_TL(2, u - u0);                                     // operands landed
         ptx::tc_fence_after_sync();
         const uint32_t w_addr = smem_base + stage * C::kStageBytes;
         const uint64_t w_desc = ptx::umma_desc_k128(w_addr);
@@ -283,6 +291,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
           ptx::umma_f8(d, w_desc + 2u * k4, a_desc + 2u * k4, idesc, k4 > 0);
         ptx::umma_commit(ptx::smem_u32(&tail->empty[stage]));
         ptx::umma_commit(ptx::smem_u32(&tail->tmem_full[buf]));
+        BFP8_TL(3, u - u0);                                     // MMAs and commits issued
         stage += C::kIssuers;
         if (stage >= C::kStages) { stage -= C::kStages; phase ^= 1u; }
       }
@@ -331,7 +340,10 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
                 if (swiglu) tail->scale_up[buf][lane + 32 * q] = va[i][q] * vu[kSwiGLU ? i : 0];
               }
             __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&tail->tmem_full[buf]));
+            if (lane == 0) {
+              ptx::mbar_arrive(ptx::smem_u32(&tail->tmem_full[buf]));
+              BFP8_TL(7, u - u0);                               // scale products parked
+            }
             if (u + kScaleAhead < u1) fetch(va[i], vw[i], vu[kSwiGLU ? i : 0]);
             ++kb;
           }
@@ -451,11 +463,13 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     };
     for (; u < u1; ++u, ++kb) {
       if (++g == G) { g = 0; ++tile; }
+      if (threadIdx.x == 0) BFP8_TL(4, u - u0);                 // epilogue turns to the unit
       const uint32_t buf = kb % kAccBufs, acc_phase = (kb / kAccBufs) & 1u;
       // uniform across the warp before the warp-collective TMEM loads
       ok = __all_sync(0xffffffffu,
                       ptx::mbar_wait(ptx::smem_u32(&tail->tmem_full[buf]), acc_phase, abort_flag, p.wait_limit));
       if (!ok) break;
+      if (threadIdx.x == 0) BFP8_TL(5, u - u0);                 // accumulator and scales ready
       ptx::tc_fence_after_sync();
       const uint32_t taddr = tmem_base + lane_addr + buf * MP;
       constexpr int kChunk = MP < 64 ? MP : 64;                  // columns fetched per TMEM round trip
@@ -480,6 +494,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
           ptx::tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&tail->tmem_empty[buf]));
+          if (threadIdx.x == 0) BFP8_TL(6, u - u0);             // buffer handed back
         }
 #pragma unroll
         for (int c = 0; c < kChunk / 16; ++c)
@@ -559,6 +574,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   ptx::tc_fence_before_sync();
   __syncthreads();
   ptx::tc_fence_after_sync();
+  BFP8_TL_DUMP(g_timeline_smallm);
   ptx::idle_after_abort(abort_flag);
   if (warp == kEpiWarps + 1) ptx::tmem_dealloc(tmem_base, C::kTmemCols);
   if (threadIdx.x == 0 && tail->abort_flag != 0) atomicOr(p.status, BFP8_STATUS_WAIT_TIMEOUT);
@@ -833,3 +849,13 @@ extern "C" int bfp8_gemm_block128_noalloc(const uint8_t* a_codes, int64_t lda, c
   return launch_gemm_smallm(a_codes, lda, a_scales, ldsa, w_codes, ldw, w_scales, bias, out, out_dtype, ldo, m, n, k,
                             scratch, status_dev, /*wait_limit=*/2000000000LL, kNoAllocMaxCtas, /*inter=*/0, /*push=*/nullptr, st);
 }
+
+#ifdef BFP8_TIMELINE
+// Diagnostic build only: the timeline of CTA kTimelineCta of the last small-M launch on the current device
+// ([kTimelineEvents][kTimelineUnits] %clock values; 0 = not reached).  Synchronises the device.
+extern "C" int bfp8_timeline_read_smallm(unsigned int* dst_host) {
+  BFP8_CUDA_TRY(cudaDeviceSynchronize());
+  BFP8_CUDA_TRY(cudaMemcpyFromSymbol(dst_host, bfp8::g_timeline_smallm, sizeof(unsigned int) * bfp8::kTimelineEvents * bfp8::kTimelineUnits));
+  return BFP8_OK;
+}
+#endif

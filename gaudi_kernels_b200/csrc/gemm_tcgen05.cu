@@ -33,6 +33,10 @@ namespace bfp8 {
 
 namespace {
 
+#ifdef BFP8_TIMELINE
+__device__ unsigned int g_timeline_large[kTimelineEvents * kTimelineUnits];
+#endif
+
 constexpr int BM = 128;            // tile rows (A rows, TMEM lanes)
 constexpr int BN = 256;            // tile columns (W rows, TMEM columns per buffer)
 constexpr int BK = 128;            // one scale block of K
@@ -107,6 +111,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 gemm_block128_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
                      const __grid_constant__ CUtensorMap tmap_out, const __grid_constant__ PushMaps pmaps,
                      const GemmParams p) {
+  BFP8_TL_DECL
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
@@ -147,6 +152,7 @@ gemm_block128_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
+      long long pkb = 0;                                        // running K block number (timeline build only)
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         int tm, tn;
@@ -154,6 +160,8 @@ gemm_block128_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         for (int g = 0; g < G; ++g) {
           ok = ptx::mbar_wait(ptx::smem_u32(&tail->done[stage]), phase ^ 1u, abort_flag, p.wait_limit);
           if (!ok) break;
+          BFP8_TL(0, pkb);                                      // stage free, copies issued
+          ++pkb;
           const uint32_t full = ptx::smem_u32(&tail->full[stage]);
           const uint32_t a_dst = smem_base + stage * kStageBytes;
           ptx::mbar_arrive_expect_tx(full, kStageBytes);
@@ -174,6 +182,7 @@ gemm_block128_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       for (long long kb = parity; kb < total; kb += 2) {
         const uint32_t stage = static_cast<uint32_t>(kb) & (kStages - 1), phase = static_cast<uint32_t>(kb >> 2) & 1u;
         if (!ptx::mbar_wait(ptx::smem_u32(&tail->full[stage]), phase, abort_flag, p.wait_limit)) break;
+        BFP8_TL(1, kb);                                         // operands landed and TMEM buffer handed back
         ptx::tc_fence_after_sync();
         const uint32_t a_addr = smem_base + stage * kStageBytes;
         const uint64_t a_desc = ptx::umma_desc_k128(a_addr);
@@ -182,6 +191,7 @@ gemm_block128_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         for (int k4 = 0; k4 < BK / 32; ++k4)   // +32 bytes along K = +2 in the descriptor's address field
           ptx::umma_f8(d, a_desc + 2u * k4, b_desc + 2u * k4, idesc, k4 > 0);
         ptx::umma_commit(ptx::smem_u32(&tail->done[stage]));
+        BFP8_TL(2, kb);                                         // MMAs and commit issued
       }
     }
    }
@@ -254,6 +264,7 @@ gemm_block128_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         const float2 sv_up = make_float2(s_up, s_up);
         ptx::tmem_wait_ld32(ra);
         ptx::tmem_regs_ready32(rb);
+        if (threadIdx.x == 0) BFP8_TL(3, kb);                   // first 64 columns in registers
         {
 #pragma unroll
           for (int j = 0; j < 16; ++j)
@@ -272,6 +283,7 @@ gemm_block128_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         ptx::tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&tail->full[(kb + 2) & (kStages - 1)]));
+        if (threadIdx.x == 0) BFP8_TL(4, kb);                   // buffer handed back
         {
 #pragma unroll
           for (int j = 0; j < 16; ++j)
@@ -280,12 +292,14 @@ gemm_block128_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           for (int j = 0; j < 16; ++j)
             acc[48 + j] = __ffma2_rn(make_float2(__uint_as_float(rb[2 * j]), __uint_as_float(rb[2 * j + 1])), sv_up, acc[48 + j]);
         }
+        if (threadIdx.x == 0) BFP8_TL(5, kb);                   // FMAs of the block issued
         if (g + 1 < G) {
           // first half of the next K block's buffer
           const uint32_t nkb = kb + 1, nbuf = nkb & 1u;
           ok = __all_sync(0xffffffffu, ptx::mbar_wait(ptx::smem_u32(&tail->done[nkb & (kStages - 1)]), (nkb >> 2) & 1u,
                                                       abort_flag, p.wait_limit));
           if (!ok) break;
+          if (threadIdx.x == 0) BFP8_TL(6, kb);                 // completion of the next block observed
           ptx::tc_fence_after_sync();
             const uint32_t naddr = tmem_base + lane_addr + nbuf * BN + wg * 128;
           ptx::tmem_ld32(naddr, ra);
@@ -400,6 +414,7 @@ gemm_block128_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   ptx::tc_fence_before_sync();
   __syncthreads();
   ptx::tc_fence_after_sync();
+  BFP8_TL_DUMP(g_timeline_large);
   ptx::idle_after_abort(abort_flag);
   if (warp == kEpiWarps + 1) ptx::tmem_dealloc(tmem_base, kTmemCols);
   if (threadIdx.x == 0 && tail->abort_flag != 0) atomicOr(p.status, BFP8_STATUS_WAIT_TIMEOUT);
@@ -526,3 +541,13 @@ int launch_gemm_large(const uint8_t* a_codes, int64_t lda, const float* a_scales
 }
 
 }  // namespace bfp8
+
+#ifdef BFP8_TIMELINE
+// Diagnostic build only: the timeline of CTA kTimelineCta of the last large-tile launch on the current device
+// ([kTimelineEvents][kTimelineUnits] %clock values per K block; 0 = not reached).  Synchronises the device.
+extern "C" int bfp8_timeline_read_large(unsigned int* dst_host) {
+  BFP8_CUDA_TRY(cudaDeviceSynchronize());
+  BFP8_CUDA_TRY(cudaMemcpyFromSymbol(dst_host, bfp8::g_timeline_large, sizeof(unsigned int) * bfp8::kTimelineEvents * bfp8::kTimelineUnits));
+  return BFP8_OK;
+}
+#endif
