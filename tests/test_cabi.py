@@ -44,6 +44,18 @@ def test_version_and_error_strings(lib):
     assert lib.bfp8_gemm_block128_workspace_bytes(8192, 14336, 4096) >= 0
 
 
+def test_weights_at_rest_switch_is_host_state(lib):
+    # a process-wide flag: returns the previous setting, off by default, touches no device
+    prev = lib.bfp8_set_weights_at_rest(0)
+    try:
+        assert lib.bfp8_set_weights_at_rest(1) == 0
+        assert lib.bfp8_set_weights_at_rest(5) == 1           # any non-zero value means "at rest"
+        assert lib.bfp8_set_weights_at_rest(0) == 1
+        assert lib.bfp8_set_weights_at_rest(0) == 0
+    finally:
+        lib.bfp8_set_weights_at_rest(prev)
+
+
 def test_host_side_argument_checks_launch_nothing(lib):
     # all of these are rejected before any CUDA call, so they are safe without a device
     assert lib.bfp8_reencode_half(None, None, 16, None, None, 0, None, None, None) == -1
