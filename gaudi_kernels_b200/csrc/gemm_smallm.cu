@@ -146,14 +146,21 @@ __device__ __forceinline__ void swiglu_finish(const Params& p, uint16_t* ex, int
     if (j < rows) mine[j * 64 + o] = static_cast<uint16_t>(float_to_bf16_bits(v[j] + b));
   asm volatile("bar.sync 1, 128;" ::: "memory");
   if (write) {
+    // all products first, without a condition in the loop, so that the exp / reciprocal chains of the rows overlap
+    // (with the bounds check inside, the rows were evaluated one after the other: 3.3 us of a 31 us launch at M = 64);
+    // rows beyond `rows` read whatever the exchange area holds and are not stored
+    uint16_t r[kRows / 2];
+#pragma unroll
+    for (int jj = 0; jj < kRows / 2; ++jj) {
+      const int j = 2 * jj + (gate ? 0 : 1);
+      const float g = bf16_bits_to_float(ex[j * 64 + o]), u = bf16_bits_to_float(ex[kRows * 64 + j * 64 + o]);
+      r[jj] = static_cast<uint16_t>(float_to_bf16_bits(silu_mul(g, u)));
+    }
     uint16_t* out = reinterpret_cast<uint16_t*>(p.out) + col;
 #pragma unroll
     for (int jj = 0; jj < kRows / 2; ++jj) {
       const int j = 2 * jj + (gate ? 0 : 1);
-      if (j < rows && j0 + j < p.m) {
-        const float g = bf16_bits_to_float(ex[j * 64 + o]), u = bf16_bits_to_float(ex[kRows * 64 + j * 64 + o]);
-        out[static_cast<int64_t>(j0 + j) * p.ldo] = static_cast<uint16_t>(float_to_bf16_bits(silu_mul(g, u)));
-      }
+      if (j < rows && j0 + j < p.m) out[static_cast<int64_t>(j0 + j) * p.ldo] = r[jj];
     }
   }
   asm volatile("bar.sync 1, 128;" ::: "memory");             // `ex` may be rewritten
