@@ -545,11 +545,11 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         for (int jj0 = 0; jj0 < rows_per; jj0 += kRound) {
           float v[kRound];
 #pragma unroll
-          for (int q = 0; q < kRound; ++q) {
-            float sum = 0.0f;
-            if (jj0 + q < rows_per)
-              for (int r = 0; r < cs; ++r) sum += mine[(r * rows_per + jj0 + q) * BN + wrow];   // rank order = K order
-            v[q] = sum;
+          for (int q = 0; q < kRound; ++q) v[q] = 0.0f;
+          for (int r = 0; r < cs; ++r) {                           // rank order = K order; the rows' sums side by side
+#pragma unroll
+            for (int q = 0; q < kRound; ++q)
+              if (jj0 + q < rows_per) v[q] += mine[(r * rows_per + jj0 + q) * BN + wrow];
           }
           swiglu_finish<kRound>(p, swiglu_ex, static_cast<int>(ctile), wrow, v, crank * rows_per + jj0,
                                 min(kRound, rows_per - jj0), ok);
@@ -557,16 +557,26 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
       } else if (ok && col < p.n) {
         const float b = p.bias != nullptr ? __ldg(p.bias + col) : 0.0f;
         const float* mine = reinterpret_cast<const float*>(smem);
-        for (int jj = 0; jj < rows_per; ++jj) {
-          const int j = crank * rows_per + jj;
-          if (j >= p.m) break;
-          float sum = 0.0f;
-          for (int r = 0; r < cs; ++r) sum += mine[(r * rows_per + jj) * BN + wrow];   // rank order = K order
-          sum += b;
-          if (p.out_bf16)
-            out_row_bf16(p, j)[col] = static_cast<uint16_t>(float_to_bf16_bits(sum));
-          else
-            reinterpret_cast<float*>(p.out)[static_cast<int64_t>(j) * p.ldo + col] = sum;
+        // four rows at a time, their sums formed side by side (each is a chain of cs dependent shared-memory loads
+        // and adds; one row after the other leaves the thread waiting on every link of every chain)
+        for (int jj0 = 0; jj0 < rows_per; jj0 += 4) {
+          float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+          for (int r = 0; r < cs; ++r) {                           // rank order = K order
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+              if (jj0 + q < rows_per) sum[q] += mine[(r * rows_per + jj0 + q) * BN + wrow];
+          }
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const int j = crank * rows_per + jj0 + q;
+            if (jj0 + q < rows_per && j < p.m) {
+              const float v = sum[q] + b;
+              if (p.out_bf16)
+                out_row_bf16(p, j)[col] = static_cast<uint16_t>(float_to_bf16_bits(v));
+              else
+                reinterpret_cast<float*>(p.out)[static_cast<int64_t>(j) * p.ldo + col] = v;
+            }
+          }
         }
       }
     }
