@@ -216,7 +216,7 @@ gemm_channel_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           // every column of the buffer has been read: release it to the MMA warp
           ptx::tc_fence_before_sync();
           __syncwarp();
-          if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&tail->tmem_empty[buf]));
+          ptx::mbar_arrive_lane0(ptx::smem_u32(&tail->tmem_empty[buf]), lane);
         }
         if (kOutBf16) {
           const int box = c >> 1;                        // one TMA box = 64 columns = two chunks

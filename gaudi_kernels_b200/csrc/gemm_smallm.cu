@@ -347,10 +347,8 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
                 if (swiglu) tail->scale_up[buf][lane + 32 * q] = va[i][q] * vu[kSwiGLU ? i : 0];
               }
             __syncwarp();
-            if (lane == 0) {
-              ptx::mbar_arrive(ptx::smem_u32(&tail->tmem_full[buf]));
-              BFP8_TL(7, u - u0);                               // scale products parked
-            }
+            ptx::mbar_arrive_lane0(ptx::smem_u32(&tail->tmem_full[buf]), lane);
+            if (lane == 0) BFP8_TL(7, u - u0);                  // scale products parked
             if (u + kScaleAhead < u1) fetch(va[i], vw[i], vu[kSwiGLU ? i : 0]);
             ++kb;
           }
@@ -500,7 +498,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
           // front of the next unit's poll
           ptx::tc_fence_before_sync();
           __syncwarp();
-          if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&tail->tmem_empty[buf]));
+          ptx::mbar_arrive_lane0(ptx::smem_u32(&tail->tmem_empty[buf]), lane);
           if (threadIdx.x == 0) BFP8_TL(6, u - u0);             // buffer handed back
         }
 #pragma unroll

@@ -282,7 +282,7 @@ gemm_block128_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         // every column of this buffer is in registers: hand it back to the MMA warp
         ptx::tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&tail->full[(kb + 2) & (kStages - 1)]));
+        ptx::mbar_arrive_lane0(ptx::smem_u32(&tail->full[(kb + 2) & (kStages - 1)]), lane);
         if (threadIdx.x == 0) BFP8_TL(4, kb);                   // buffer handed back
         {
 #pragma unroll
