@@ -110,6 +110,14 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
 __device__ __forceinline__ void mbar_arrive_remote(uint32_t bar_cluster) {
   asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster) : "memory");
 }
+// The same from lane 0 only, as a predicated instruction (the warp does not branch; see ptx::mbar_arrive_lane0).
+__device__ __forceinline__ void mbar_arrive_remote_lane0(uint32_t bar_cluster, int lane) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.eq.s32 p, %1, 0;\n\t"
+      "@p mbarrier.arrive.shared::cluster.b64 _, [%0];\n\t}"
+      ::"r"(bar_cluster), "r"(lane) : "memory");
+}
 __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -318,7 +326,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           // all of this thread's columns of the buffer are in registers: release it to the MMA issuer
           ptx::tc_fence_before_sync();
           __syncwarp();
-          if (lane == 0) mbar_arrive_remote(map_to_cta(ptx::smem_u32(&tail->tmem_empty[buf]), 0));
+          mbar_arrive_remote_lane0(map_to_cta(ptx::smem_u32(&tail->tmem_empty[buf]), 0), lane);
           fma32(acc + half * 32, ra, sv);
           // next buffer in program order: the right half of this K block, or the left half of the next
           const bool has_next = (half == 0) || (g + 1 < G);
